@@ -1,0 +1,485 @@
+// Block scoring for sm_100a: dense Q.K^T on tcgen05 with TMEM accumulators,
+// K tiles staged by TMA, softmax mass accumulated per score block.
+//
+// Replaces block_score_kernel / block_normalize_kernel of the reference
+// (flash_topk_attn_v2/csrc/block_score_kernel.cu:19-314).
+//
+// One CTA owns 256 query rows of one (batch, head) slice and streams every
+// key tile once.  Roles: warp 0 = TMA producer, warp 1 = UMMA issuer, warps
+// 2..9 = 256 softmax threads, one query row each (TMEM lane == row).
+// Two 128x128 fp32 accumulators per stage (rows 0-127 / 128-255 share the K
+// tile), two stages, so the tensor core works on tile t+1 while the softmax
+// threads drain tile t: 4 x 128 = 512 TMEM columns.
+//
+// Softmax is single pass against a fixed per-row reference exponent `mref`
+// (an integer in log2 units): sum_j[t] = sum_{i in block j} 2^(c*s_ti - mref),
+// L[t] = sum_j sum_j[t]; the block score is sum_j / L.  mref comes from the
+// row maximum over the first key tile (mode 0).  Should any later logit
+// exceed it by more than the fp32 exponent range the row total overflows;
+// the kernel then raises `*fallback` and the launcher's two follow-up
+// launches (mode 1: exact row maximum, mode 2: sums against it) redo the work.
+// They return at once when the flag is clear.
+#include <algorithm>
+#include <cmath>
+
+#include "ftk_host.cuh"
+#include "ftk_sm100.cuh"
+
+namespace ftk {
+
+constexpr int SC_QROWS = 256;      // query rows per CTA
+constexpr int SC_KT = 128;         // key rows per tile (UMMA N)
+constexpr int SC_STAGES = 4;       // K tile ring depth
+constexpr int SC_THREADS = 320;    // 2 + 8 warps
+constexpr int SC_CHUNK_BYTES = 128 * 128;  // 128 rows x 64 16-bit elements
+
+struct ScoreParams {
+  int N, M, D;
+  int bsz, pad_head;          // score block size, virtual head padding
+  int tile_rows;              // rows fetched per K tile (TMA box rows)
+  int blocks_per_tile;        // bsz <= 128: whole blocks per tile, else 0
+  int tiles_per_block;        // bsz > 128: tiles per block, else 0
+  int num_tiles;
+  int fmt;                    // 0 fp16, 1 bf16
+  int mode;                   // 0 first-tile reference, 1 row max only, 2 given reference
+  int H, bh_begin;
+  float scale_log2;           // log2(e) / sqrt(D)
+  float* sums;                // [bh_count][N][M]   unnormalised block sums
+  float* row_total;           // [bh_count][N]      L
+  float* row_max;             // [bh_count][N]      raw-logit row maximum (modes 1, 2)
+  int* fallback;              // device flag
+  int* status;
+};
+
+struct TileInfo {
+  int row0;     // first key token of the tile (may be negative)
+  int used;     // accumulator columns that belong to score blocks
+  int block0;   // score block of column 0
+  int col_in_block0;  // position of column 0 inside that block
+};
+
+__device__ __forceinline__ TileInfo tile_info(const ScoreParams& p, int t) {
+  TileInfo ti;
+  if (p.blocks_per_tile > 0) {
+    ti.block0 = t * p.blocks_per_tile;
+    int nb = min(p.blocks_per_tile, p.M - ti.block0);
+    ti.row0 = ti.block0 * p.bsz - p.pad_head;
+    ti.used = nb * p.bsz;
+    ti.col_in_block0 = 0;
+  } else {
+    int j = t / p.tiles_per_block, part = t - j * p.tiles_per_block;
+    ti.block0 = j;
+    ti.row0 = j * p.bsz - p.pad_head + part * SC_KT;
+    ti.used = min(SC_KT, p.bsz - part * SC_KT);
+    ti.col_in_block0 = part * SC_KT;
+  }
+  return ti;
+}
+
+template <int D>
+__global__ void __launch_bounds__(SC_THREADS, 1)
+score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+             const ScoreParams p) {
+  constexpr int NCH = D / 64;                       // 128-byte chunks per row
+  constexpr int Q_BYTES = 2 * NCH * SC_CHUNK_BYTES; // 256 rows
+  constexpr int K_STAGE_BYTES = NCH * SC_CHUNK_BYTES;
+
+  if (p.mode != 0 && *p.fallback == 0) return;  // uniform: follow-up launches idle
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + Q_BYTES;
+  __shared__ __align__(8) uint64_t bars[1 + 2 * SC_STAGES + 4];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int q0 = blockIdx.x * SC_QROWS;
+  const int bh_local = blockIdx.y;
+  const int bh = p.bh_begin + bh_local;
+  const int b_idx = bh / p.H, h_idx = bh - b_idx * p.H;
+
+  const uint32_t bar_q = smem_u32(&bars[0]);
+  auto bar_kfull = [&](int s) { return smem_u32(&bars[1 + s]); };
+  auto bar_kempty = [&](int s) { return smem_u32(&bars[1 + SC_STAGES + s]); };
+  auto bar_afull = [&](int s) { return smem_u32(&bars[1 + 2 * SC_STAGES + s]); };
+  auto bar_aempty = [&](int s) { return smem_u32(&bars[1 + 2 * SC_STAGES + 2 + s]); };
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(bar_q, 1);
+    for (int s = 0; s < SC_STAGES; s++) {
+      mbar_init(bar_kfull(s), 1);
+      mbar_init(bar_kempty(s), 1);
+    }
+    for (int s = 0; s < 2; s++) {
+      mbar_init(bar_afull(s), 1);
+      mbar_init(bar_aempty(s), 8);  // one arrival per softmax warp
+    }
+    mbar_init_fence();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_base_s), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  WaitCtx w{&abort_flag, p.status};
+  const int T = p.num_tiles;
+
+  if (warp == 0) {
+    // ------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(bar_q, Q_BYTES);
+      for (int half = 0; half < 2; half++)
+        for (int c = 0; c < NCH; c++)
+          tma_load_4d(smem_u32(sQ) + (half * NCH + c) * SC_CHUNK_BYTES, &tm_q, bar_q, c * 64,
+                      h_idx, q0 + half * 128, b_idx);
+      const uint32_t tile_bytes = static_cast<uint32_t>(p.tile_rows) * 128u * NCH;
+      for (int t = 0; t < T; t++) {
+        const int s = t % SC_STAGES;
+        const uint32_t ph = (t / SC_STAGES) & 1;
+        if (!mbar_wait(bar_kempty(s), ph ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
+        const TileInfo ti = tile_info(p, t);
+        mbar_expect_tx(bar_kfull(s), tile_bytes);
+        for (int c = 0; c < NCH; c++)
+          tma_load_4d(smem_u32(sK) + s * K_STAGE_BYTES + c * SC_CHUNK_BYTES, &tm_k, bar_kfull(s),
+                      c * 64, h_idx, ti.row0, b_idx);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------- UMMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(128, SC_KT, p.fmt, 0, 0);
+      bool ok = mbar_wait(bar_q, 0, w, FTK_DEV_TIMEOUT_MMA);
+      for (int t = 0; ok && t < T; t++) {
+        const int s = t % SC_STAGES;
+        const uint32_t ph = (t / SC_STAGES) & 1;
+        const int a = t & 1;
+        const uint32_t pa = (t >> 1) & 1;
+        if (!mbar_wait(bar_aempty(a), pa ^ 1, w, FTK_DEV_TIMEOUT_MMA)) break;
+        if (!mbar_wait(bar_kfull(s), ph, w, FTK_DEV_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t kbase = smem_u32(sK) + s * K_STAGE_BYTES;
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+          const uint32_t d_tmem = tmem + static_cast<uint32_t>((a * 2 + half) * SC_KT);
+          const uint32_t qbase = smem_u32(sQ) + half * NCH * SC_CHUNK_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ks++) {
+            const uint32_t off = (ks / 4) * SC_CHUNK_BYTES + (ks % 4) * 32;
+            umma_ss(d_tmem, smem_desc_sw128(qbase + off, 16, 1024),
+                    smem_desc_sw128(kbase + off, 16, 1024), idesc, ks > 0);
+          }
+        }
+        umma_commit(bar_kempty(s));  // smem stage reusable once these UMMAs retire
+        umma_commit(bar_afull(a));   // accumulators readable
+      }
+    }
+  } else {
+    // ---------------------------------------------------- softmax threads
+    const int cw = warp - 2;               // 0..7
+    const int half = cw >> 2;              // which 128-row accumulator
+    const int quarter = warp & 3;          // TMEM lane quarter this warp may read
+    const int row_in_cta = half * 128 + quarter * 32 + lane;
+    const int row = q0 + row_in_cta;
+    const bool row_ok = row < p.N;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    const size_t row_off = (static_cast<size_t>(bh_local) * p.N + (row_ok ? row : 0));
+    float* out_row = p.sums + row_off * p.M;
+    const float c = p.scale_log2;
+
+    float mref = 0.f;
+    float run_max = -INFINITY;
+    float total = 0.f;
+    bool ok = true;
+
+    if (p.mode == 2) mref = ceilf(p.row_max[row_off] * c);
+
+    if (p.mode == 0) {
+      // reference exponent from the row maximum over the first key tile
+      ok = mbar_wait(bar_afull(0), 0, w, FTK_DEV_TIMEOUT_CONSUMER);
+      if (ok) {
+        tc_fence_after();
+        const TileInfo ti = tile_info(p, 0);
+        const int lo = max(0, -ti.row0), hi = min(ti.used, p.N - ti.row0);
+        float mx = -INFINITY;
+        for (int c0 = 0; c0 < ti.used; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(lane_addr + static_cast<uint32_t>(half * SC_KT + c0), r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i++) {
+            const int col = c0 + i;
+            if (col >= lo && col < hi) mx = fmaxf(mx, __uint_as_float(r[i]));
+          }
+        }
+        mref = ceilf(mx * c);
+        if (!(fabsf(mref) < 1e30f)) mref = 0.f;
+      }
+    }
+
+    float acc = 0.f;
+    int j = 0, col_in_block = 0;
+    for (int t = 0; ok && t < T; t++) {
+      const int a = t & 1;
+      const uint32_t pa = (t >> 1) & 1;
+      if (!mbar_wait(bar_afull(a), pa, w, FTK_DEV_TIMEOUT_CONSUMER)) { ok = false; break; }
+      tc_fence_after();
+      const TileInfo ti = tile_info(p, t);
+      const int lo = max(0, -ti.row0), hi = min(ti.used, p.N - ti.row0);
+      const bool full = (lo == 0 && hi == ti.used);
+      if (ti.col_in_block0 == 0) { j = ti.block0; col_in_block = 0; }
+      const uint32_t acc_addr = lane_addr + static_cast<uint32_t>((a * 2 + half) * SC_KT);
+      for (int c0 = 0; c0 < ti.used; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(acc_addr + static_cast<uint32_t>(c0), r);
+        tmem_wait_ld();
+        if (c0 + 32 >= ti.used) {
+          // last chunk of the tile is in registers: hand the accumulator back
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_aempty(a));
+        }
+#pragma unroll
+        for (int hc = 0; hc < 2; hc++) {
+          const int cb = c0 + hc * 16;
+          if (cb < ti.used) {
+            if (p.mode == 1) {
+#pragma unroll
+              for (int i = 0; i < 16; i++) {
+                const int col = cb + i;
+                if (full || (col >= lo && col < hi))
+                  run_max = fmaxf(run_max, __uint_as_float(r[hc * 16 + i]));
+              }
+            } else {
+              float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+              if (full) {
+#pragma unroll
+                for (int i = 0; i < 16; i += 4) {
+                  a0 += fast_exp2(fmaf(__uint_as_float(r[hc * 16 + i + 0]), c, -mref));
+                  a1 += fast_exp2(fmaf(__uint_as_float(r[hc * 16 + i + 1]), c, -mref));
+                  a2 += fast_exp2(fmaf(__uint_as_float(r[hc * 16 + i + 2]), c, -mref));
+                  a3 += fast_exp2(fmaf(__uint_as_float(r[hc * 16 + i + 3]), c, -mref));
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                  const int col = cb + i;
+                  if (col >= lo && col < hi)
+                    a0 += fast_exp2(fmaf(__uint_as_float(r[hc * 16 + i]), c, -mref));
+                }
+              }
+              acc += (a0 + a1) + (a2 + a3);
+              col_in_block += 16;
+              if (col_in_block == p.bsz) {
+                if (row_ok) out_row[j] = acc;
+                total += acc;
+                acc = 0.f;
+                col_in_block = 0;
+                j++;
+              }
+            }
+          }
+        }
+      }
+    }
+    if (ok && row_ok) {
+      if (p.mode == 1) {
+        p.row_max[row_off] = run_max;
+      } else {
+        p.row_total[row_off] = total;
+        if (!(total > 0.f && total < 3.0e38f)) atomicExch(p.fallback, 1);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    // give copies still in flight time to land before the smem is released
+    for (int i = 0; i < 200; i++) __nanosleep(1000);
+  }
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// block_scores[r][j] = sums[r][j] / total[r]
+__global__ void score_normalize_kernel(const float* __restrict__ sums,
+                                       const float* __restrict__ total, float* __restrict__ out,
+                                       int64_t rows, int M) {
+  const int64_t n = rows * M;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / M;
+    out[i] = __fdiv_rn(sums[i], total[r]);
+  }
+}
+
+template <int D>
+static int launch_score_d(const CUtensorMap& tq, const CUtensorMap& tk, ScoreParams p,
+                          int64_t bh_count, cudaStream_t st) {
+  constexpr int NCH = D / 64;
+  const size_t smem = 1024 + (2 * NCH + SC_STAGES * NCH) * SC_CHUNK_BYTES;
+  if (cudaFuncSetAttribute(score_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return FTK_ERR_CUDA;
+  dim3 grid((p.N + SC_QROWS - 1) / SC_QROWS, static_cast<unsigned>(bh_count));
+  for (int mode = 0; mode < 3; mode++) {
+    p.mode = mode;
+    score_kernel<D><<<grid, SC_THREADS, smem, st>>>(tq, tk, p);
+    if (cudaGetLastError() != cudaSuccess) return FTK_ERR_CUDA;
+  }
+  return FTK_OK;
+}
+
+struct ScoreWs {
+  float* row_total;
+  float* row_max;
+  int* fallback;
+  float* sums;
+};
+
+static size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+
+static size_t score_ws_layout(int64_t bh_count, int64_t N, int64_t M, bool with_sums, char* base,
+                              ScoreWs* ws) {
+  size_t off = 0;
+  const size_t rows = static_cast<size_t>(bh_count) * N;
+  if (ws) ws->fallback = reinterpret_cast<int*>(base + off);
+  off += 256;
+  if (ws) ws->row_total = reinterpret_cast<float*>(base + off);
+  off += align256(rows * 4);
+  if (ws) ws->row_max = reinterpret_cast<float*>(base + off);
+  off += align256(rows * 4);
+  if (ws) ws->sums = reinterpret_cast<float*>(base + off);
+  if (with_sums) off += align256(rows * static_cast<size_t>(M) * 4);
+  return off;
+}
+
+// Validates arguments, encodes the tensor maps and launches the three score
+// passes; sums go to `sums` ([bh_count][N][M]).
+static int run_score(const void* q, const void* k, int dtype, int64_t B, int64_t H, int64_t N,
+                     int64_t D, int64_t sq_b, int64_t sq_n, int64_t sq_h, int64_t sk_b,
+                     int64_t sk_n, int64_t sk_h, int64_t bh_begin, int64_t bh_count, int bsz,
+                     int pad_head, int pad_tail, float scale, float* sums, const ScoreWs& ws,
+                     int32_t* status, cudaStream_t st) {
+  if (!q || !k || B <= 0 || H <= 0 || N <= 0 || bsz <= 0 || !(scale > 0.f))
+    return FTK_ERR_BAD_ARG;
+  if (dtype != FTK_DTYPE_F16 && dtype != FTK_DTYPE_BF16) return FTK_ERR_BAD_ARG;
+  if (pad_head < 0 || pad_tail < 0 || pad_head >= bsz || pad_tail >= bsz) return FTK_ERR_BAD_ARG;
+  if ((pad_head + N + pad_tail) % bsz != 0) return FTK_ERR_BAD_ARG;
+  if (bh_begin < 0 || bh_count <= 0 || bh_begin + bh_count > B * H) return FTK_ERR_BAD_ARG;
+  if (D != 64 && D != 128) return FTK_ERR_UNSUPPORTED;
+  if (bsz % 16 != 0) return FTK_ERR_UNSUPPORTED;
+  if (bh_count > 65535) return FTK_ERR_BAD_ARG;
+
+  ScoreParams p{};
+  p.N = static_cast<int>(N);
+  p.M = static_cast<int>((pad_head + N + pad_tail) / bsz);
+  p.D = static_cast<int>(D);
+  p.bsz = bsz;
+  p.pad_head = pad_head;
+  if (bsz <= SC_KT) {
+    p.blocks_per_tile = SC_KT / bsz;
+    p.tiles_per_block = 0;
+    p.tile_rows = p.blocks_per_tile * bsz;
+    p.num_tiles = (p.M + p.blocks_per_tile - 1) / p.blocks_per_tile;
+  } else {
+    p.blocks_per_tile = 0;
+    p.tiles_per_block = (bsz + SC_KT - 1) / SC_KT;
+    p.tile_rows = SC_KT;
+    p.num_tiles = p.M * p.tiles_per_block;
+  }
+  p.fmt = dtype;
+  p.H = static_cast<int>(H);
+  p.bh_begin = static_cast<int>(bh_begin);
+  p.scale_log2 = static_cast<float>(1.4426950408889634 * static_cast<double>(scale));
+  p.sums = sums;
+  p.row_total = ws.row_total;
+  p.row_max = ws.row_max;
+  p.fallback = ws.fallback;
+  p.status = status;
+
+  CUtensorMap tq, tk;
+  int e = encode_tmap_bnhd(&tq, q, dtype, B, N, H, D, sq_b, sq_n, sq_h, 64, 128);
+  if (e) return e;
+  e = encode_tmap_bnhd(&tk, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, p.tile_rows);
+  if (e) return e;
+  if (cudaMemsetAsync(ws.fallback, 0, 4, st) != cudaSuccess) return FTK_ERR_CUDA;
+  if (D == 64) return launch_score_d<64>(tq, tk, p, bh_count, st);
+  return launch_score_d<128>(tq, tk, p, bh_count, st);
+}
+
+int select_launch(const float* block_scores, const float* row_scale, int64_t rows, int M,
+                  int max_topk, int bsz, int pad_head, int pad_tail, float threshold,
+                  int32_t* topk_idx, float* topk_raw, float* topk_avg, cudaStream_t st);
+
+}  // namespace ftk
+
+using namespace ftk;
+
+extern "C" size_t ftk_block_score_workspace(int64_t bh_count, int64_t N) {
+  return score_ws_layout(bh_count, N, 0, false, nullptr, nullptr);
+}
+
+extern "C" int ftk_block_score(const void* q, const void* k, int dtype, int64_t B, int64_t H,
+                               int64_t N, int64_t D, int64_t sq_b, int64_t sq_n, int64_t sq_h,
+                               int64_t sk_b, int64_t sk_n, int64_t sk_h, int64_t bh_begin,
+                               int64_t bh_count, int score_block_size, int pad_head, int pad_tail,
+                               float scale, float* block_scores, void* workspace,
+                               size_t workspace_bytes,
+                               int32_t* status, void* stream) {
+  if (!block_scores) return FTK_ERR_BAD_ARG;
+  if (bh_count <= 0 || N <= 0) return FTK_ERR_BAD_ARG;
+  if (!workspace || workspace_bytes < ftk_block_score_workspace(bh_count, N))
+    return FTK_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return FTK_ERR_BAD_ARG;
+  ScoreWs ws;
+  score_ws_layout(bh_count, N, 0, false, static_cast<char*>(workspace), &ws);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int e = run_score(q, k, dtype, B, H, N, D, sq_b, sq_n, sq_h, sk_b, sk_n, sk_h, bh_begin,
+                    bh_count, score_block_size, pad_head, pad_tail, scale, block_scores, ws, status,
+                    st);
+  if (e) return e;
+  const int M = static_cast<int>((pad_head + N + pad_tail) / score_block_size);
+  const int64_t rows = bh_count * N;
+  const int grid = static_cast<int>(std::min<int64_t>((rows * M + 255) / 256, 148 * 16));
+  score_normalize_kernel<<<grid, 256, 0, st>>>(block_scores, ws.row_total, block_scores, rows, M);
+  return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+}
+
+extern "C" size_t ftk_score_topk_workspace(int64_t bh_count, int64_t N, int64_t M) {
+  return score_ws_layout(bh_count, N, M, true, nullptr, nullptr);
+}
+
+extern "C" int ftk_score_topk(const void* q, const void* k, int dtype, int64_t B, int64_t H,
+                              int64_t N, int64_t D, int64_t sq_b, int64_t sq_n, int64_t sq_h,
+                              int64_t sk_b, int64_t sk_n, int64_t sk_h, int64_t bh_begin,
+                              int64_t bh_count, int score_block_size, int pad_head, int pad_tail,
+                              float scale, int topk, float threshold, int32_t* topk_idx, float* topk_raw,
+                              float* topk_avg, void* workspace, size_t workspace_bytes,
+                              int32_t* status, void* stream) {
+  if (!topk_idx || !topk_raw || !topk_avg || topk < 0) return FTK_ERR_BAD_ARG;
+  if (bh_count <= 0 || N <= 0 || score_block_size <= 0) return FTK_ERR_BAD_ARG;
+  const int64_t M = (pad_head + N + pad_tail) / score_block_size;
+  if (M > 4096) return FTK_ERR_UNSUPPORTED;
+  if (!workspace || workspace_bytes < ftk_score_topk_workspace(bh_count, N, M))
+    return FTK_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return FTK_ERR_BAD_ARG;
+  ScoreWs ws;
+  score_ws_layout(bh_count, N, M, true, static_cast<char*>(workspace), &ws);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int e = run_score(q, k, dtype, B, H, N, D, sq_b, sq_n, sq_h, sk_b, sk_n, sk_h, bh_begin,
+                    bh_count, score_block_size, pad_head, pad_tail, scale, ws.sums, ws, status, st);
+  if (e) return e;
+  return select_launch(ws.sums, ws.row_total, bh_count * N, static_cast<int>(M), topk,
+                       score_block_size, pad_head, pad_tail, threshold, topk_idx, topk_raw,
+                       topk_avg, st);
+}

@@ -1,0 +1,550 @@
+// HBM-bound integer / fp32 kernels of the path: top-k select, q-block merge,
+// reverse index, count sort.  No tensor cores here; the rules that matter are
+// coalesced row reads, warp-level reductions and a fixed summation order so
+// that every result is reproducible bit for bit.
+#include <algorithm>
+
+#include "ftk_host.cuh"
+#include "ftk_sm100.cuh"
+
+namespace ftk {
+
+__device__ __forceinline__ int redux_max_s32(int v) {
+  int r;
+  asm volatile("redux.sync.max.s32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
+  return r;
+}
+__device__ __forceinline__ unsigned redux_min_u32(unsigned v) {
+  unsigned r;
+  asm volatile("redux.sync.min.u32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
+  return r;
+}
+
+// ------------------------------------------------------------------ select
+// One warp per row.  Replaces topk_select_kernel
+// (flash_topk_attn_v2/csrc/topk_select_kernel.cu:7-131): average = raw /
+// valid_count (IEEE division), order by (average descending, block id
+// ascending), sequential fp32 running sum of the raw scores, keep positions up
+// to and including the first whose running sum reaches the threshold.
+// The row's averages and raw scores sit in shared memory (block id = index);
+// lane l owns ids l, l+32, ...  Each round takes the warp-wide best of the
+// per-lane bests with two redux instructions and the owning lane rescans its
+// own ids.  Scores are non-negative, so their bit patterns order as integers;
+// consumed / absent entries hold -1.0f.
+constexpr int SEL_WARPS = 8;
+
+__global__ void __launch_bounds__(SEL_WARPS * 32)
+topk_select_kernel(const float* __restrict__ scores, const float* __restrict__ row_scale,
+                   int64_t rows, int M, int M_out, int bsz, int pad_head, int pad_tail,
+                   float threshold, int32_t* __restrict__ out_idx, float* __restrict__ out_raw,
+                   float* __restrict__ out_avg) {
+  extern __shared__ float sel_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * SEL_WARPS + warp;
+  if (row >= rows) return;
+  const int Mp = (M + 31) & ~31;
+  float* savg = sel_smem + static_cast<size_t>(warp) * 2 * Mp;
+  float* sraw = savg + Mp;
+  const float* in = scores + row * M;
+  const float denom = row_scale ? row_scale[row] : 1.f;
+
+  int best_bits = __float_as_int(-1.f);
+  int best_j = 0x7fffffff;
+  for (int j = lane; j < Mp; j += 32) {
+    float raw = 0.f, avg = -1.f;
+    if (j < M) {
+      raw = in[j];
+      if (row_scale) raw = __fdiv_rn(raw, denom);
+      int n = bsz;
+      if (j == 0) n -= pad_head;
+      if (j == M - 1) n -= pad_tail;
+      avg = __fdiv_rn(raw, static_cast<float>(n));
+      if (!(avg >= 0.f)) avg = 0.f;  // NaN / negative input: rank last among real blocks
+    }
+    savg[j] = avg;
+    sraw[j] = raw;
+    const int bits = __float_as_int(avg);
+    if (bits > best_bits) { best_bits = bits; best_j = j; }
+  }
+  __syncwarp();
+
+  float cum = 0.f;
+  bool cut = false;
+  int32_t* oi = out_idx + row * M_out;
+  float* orw = out_raw + row * M_out;
+  float* oav = out_avg + row * M_out;
+  int hold_idx = -1;
+  float hold_raw = 0.f, hold_avg = 0.f;
+  for (int r = 0; r < M_out; r++) {
+    int w_idx = -1;
+    float w_raw = 0.f, w_avg = 0.f;
+    if (!cut) {
+      const int mx = redux_max_s32(best_bits);
+      const unsigned cand = (best_bits == mx) ? static_cast<unsigned>(best_j) : 0xffffffffu;
+      const unsigned win = redux_min_u32(cand);
+      w_idx = static_cast<int>(win);
+      w_raw = sraw[win];
+      w_avg = __int_as_float(mx);
+      cum += w_raw;
+      if (cum >= threshold) cut = true;
+      if ((win & 31u) == static_cast<unsigned>(lane)) {
+        savg[win] = -1.f;
+        best_bits = __float_as_int(-1.f);
+        best_j = 0x7fffffff;
+        for (int j = lane; j < Mp; j += 32) {
+          const int bits = __float_as_int(savg[j]);
+          if (bits > best_bits) { best_bits = bits; best_j = j; }
+        }
+      }
+    }
+    if ((r & 31) == lane) { hold_idx = w_idx; hold_raw = w_raw; hold_avg = w_avg; }
+    if ((r & 31) == 31 || r == M_out - 1) {
+      const int base = r & ~31;
+      if (base + lane <= r) {
+        oi[base + lane] = hold_idx;
+        orw[base + lane] = hold_raw;
+        oav[base + lane] = hold_avg;
+      }
+    }
+  }
+}
+
+int select_launch(const float* block_scores, const float* row_scale, int64_t rows, int M,
+                  int max_topk, int bsz, int pad_head, int pad_tail, float threshold,
+                  int32_t* topk_idx, float* topk_raw, float* topk_avg, cudaStream_t st) {
+  if (!block_scores || !topk_idx || !topk_raw || !topk_avg) return FTK_ERR_BAD_ARG;
+  if (rows <= 0 || M <= 0 || bsz <= 0 || max_topk < 0) return FTK_ERR_BAD_ARG;
+  if (pad_head < 0 || pad_tail < 0 || pad_head >= bsz || pad_tail >= bsz) return FTK_ERR_BAD_ARG;
+  if (M > 4096) return FTK_ERR_UNSUPPORTED;
+  const int M_out = max_topk > 0 ? std::min(max_topk, M) : M;
+  const int Mp = (M + 31) & ~31;
+  const size_t smem = static_cast<size_t>(SEL_WARPS) * 2 * Mp * sizeof(float);
+  if (smem > 48 * 1024) {
+    if (cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return FTK_ERR_CUDA;
+  }
+  const int64_t grid = (rows + SEL_WARPS - 1) / SEL_WARPS;
+  if (grid > 0x7fffffffLL) return FTK_ERR_BAD_ARG;
+  topk_select_kernel<<<static_cast<unsigned>(grid), SEL_WARPS * 32, smem, st>>>(
+      block_scores, row_scale, rows, M, M_out, bsz, pad_head, pad_tail, threshold, topk_idx,
+      topk_raw, topk_avg);
+  return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+}
+
+// ------------------------------------------------------------------- merge
+// One CTA (4 warps) per q-block.  Replaces qblock_merge_kernel
+// (flash_topk_attn_v2/csrc/qblock_merge_kernel.cu:7-89).  The reference adds
+// with shared-memory float atomics in arbitrary order; here warp w owns the
+// block ids congruent to w mod 4 and walks every entry of the q-block in
+// (row, rank) order, so each aggregate is an fp32 sum in one fixed order.
+// Entries of one 32-wide step that name the same block (possible when K < 32)
+// are applied in lane order.  The table is then sorted as 64-bit keys
+// (aggregate bits : ~block id), largest first, with a bitonic network.
+constexpr int MG_THREADS = 128;
+
+__global__ void __launch_bounds__(MG_THREADS)
+qblock_merge_kernel(const int32_t* __restrict__ idx, const float* __restrict__ scr, int64_t N,
+                    int K, int g, int q_pad_head, int QM, int Mtot, int Mp, int W,
+                    int32_t* __restrict__ out_idx, float* __restrict__ out_scr,
+                    int32_t* __restrict__ counts, int* status) {
+  extern __shared__ unsigned long long mg_keys[];
+  float* agg = reinterpret_cast<float*>(mg_keys + Mp);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t qb = blockIdx.x;  // bh * QM + m
+  const int64_t bh = qb / QM;
+  const int m = static_cast<int>(qb - bh * QM);
+
+  __shared__ int cnt_s;
+  if (tid == 0) cnt_s = 0;
+  for (int j = tid; j < Mp; j += MG_THREADS) agg[j] = 0.f;
+  __syncthreads();
+
+  const int t0 = m * g - q_pad_head;
+  const int r0 = max(t0, 0);
+  const int r1 = static_cast<int>(min(static_cast<long long>(N), static_cast<long long>(t0) + g));
+  if (r1 > r0) {
+    const int64_t base = (bh * N + r0) * K;
+    const int total = (r1 - r0) * K;
+    for (int e0 = 0; e0 < total; e0 += 32) {
+      const int e = e0 + lane;
+      int j = -1;
+      float s = 0.f;
+      if (e < total) {
+        j = idx[base + e];
+        s = scr ? scr[base + e] : 1.f;
+      }
+      if (j >= Mtot) {
+        if (status) atomicCAS(status, 0, FTK_DEV_BAD_INDEX);
+        j = -1;
+      }
+      const bool mine = (j >= 0) && ((j & 3) == warp);
+      const unsigned grp = __match_any_sync(0xffffffffu, mine ? j : -1 - lane);
+      const int rank = __popc(grp & ((1u << lane) - 1u));
+      const int rounds = redux_max_s32(mine ? __popc(grp) : 0);
+      for (int rd = 0; rd < rounds; rd++) {
+        if (mine && rank == rd) agg[j] += s;
+        __syncwarp();
+      }
+    }
+  }
+  __syncthreads();
+
+  for (int j = tid; j < Mp; j += MG_THREADS) {
+    const float a = agg[j];
+    unsigned long long key = 0ull;
+    if (j < Mtot && a > 0.f)
+      key = (static_cast<unsigned long long>(__float_as_uint(a)) << 32) |
+            static_cast<unsigned long long>(0xffffffffu - static_cast<unsigned>(j));
+    mg_keys[j] = key;
+  }
+  __syncthreads();
+  // bitonic sort, descending
+  for (int k = 2; k <= Mp; k <<= 1) {
+    for (int s = k >> 1; s > 0; s >>= 1) {
+      for (int i = tid; i < Mp; i += MG_THREADS) {
+        const int p = i ^ s;
+        if (p > i) {
+          const unsigned long long a = mg_keys[i], b = mg_keys[p];
+          const bool desc = ((i & k) == 0);
+          if (desc ? (a < b) : (a > b)) { mg_keys[i] = b; mg_keys[p] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  int local = 0;
+  int32_t* oi = out_idx + qb * W;
+  float* os = out_scr ? out_scr + qb * W : nullptr;
+  for (int r = tid; r < W; r += MG_THREADS) {
+    int id = -1;
+    float sc = 0.f;
+    if (r < Mp) {
+      const unsigned long long key = mg_keys[r];
+      if (key != 0ull) {
+        id = static_cast<int>(0xffffffffu - static_cast<unsigned>(key & 0xffffffffull));
+        sc = __uint_as_float(static_cast<unsigned>(key >> 32));
+        local++;
+      }
+    }
+    oi[r] = id;
+    if (os) os[r] = sc;
+  }
+  // count = number of valid entries written (they form a prefix of the row)
+  if (local) atomicAdd(&cnt_s, local);
+  __syncthreads();
+  if (tid == 0 && counts) counts[qb] = cnt_s;
+}
+
+__global__ void max_index_kernel(const int32_t* __restrict__ idx, int64_t n, int32_t* result) {
+  int mx = 0;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    mx = max(mx, idx[i] + 1);
+  mx = redux_max_s32(mx);
+  if ((threadIdx.x & 31) == 0) atomicMax(result, mx);
+}
+__global__ void set_one_kernel(int32_t* p) { *p = 1; }
+
+// ----------------------------------------------------------- reverse index
+// Replaces build_reverse_indices_kernel / argsort_reverse_counts_kernel
+// (flash_topk_attn_v2/csrc/build_reverse_indices_kernel.cu:6-62).  The
+// reference hands out slots with global atomicAdd (arbitrary order); here a
+// bitmap [bh][kv block][q-block bit] is OR-ed together first (order-free),
+// then one warp per kv block lists its set bits in ascending q-block order.
+__global__ void reverse_mark_kernel(const int32_t* __restrict__ merged,
+                                    const int32_t* __restrict__ counts, int64_t total_qb, int QM,
+                                    int W, int M, int words, unsigned* __restrict__ bits,
+                                    int* status) {
+  // one warp per q-block row
+  const int64_t qb = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (qb >= total_qb) return;
+  const int64_t bh = qb / QM;
+  const int m = static_cast<int>(qb - bh * QM);
+  const int cnt = counts ? min(counts[qb], W) : W;
+  const int32_t* row = merged + qb * W;
+  for (int e = lane; e < cnt; e += 32) {
+    const int j = row[e];
+    if (j < 0) continue;
+    if (j >= M) {
+      if (status) atomicCAS(status, 0, FTK_DEV_BAD_INDEX);
+      continue;
+    }
+    atomicOr(&bits[(bh * M + j) * words + (m >> 5)], 1u << (m & 31));
+  }
+}
+
+__global__ void reverse_list_kernel(const unsigned* __restrict__ bits, int64_t total_kv, int QM,
+                                    int words, int32_t* __restrict__ rev,
+                                    int32_t* __restrict__ rcount) {
+  const int64_t kv = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (kv >= total_kv) return;
+  const unsigned* wrow = bits + kv * words;
+  int32_t* out = rev + kv * QM;
+  int base = 0;
+  for (int w0 = 0; w0 < words; w0 += 32) {
+    const int wi = w0 + lane;
+    const unsigned word = wi < words ? wrow[wi] : 0u;
+    const int c = __popc(word);
+    // exclusive prefix over lanes
+    int pre = c;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, pre, d);
+      if (lane >= d) pre += v;
+    }
+    const int tot = __shfl_sync(0xffffffffu, pre, 31);
+    int pos = base + pre - c;
+    unsigned wbits = word;
+    while (wbits) {
+      const int b = __ffs(wbits) - 1;
+      wbits &= wbits - 1;
+      out[pos++] = wi * 32 + b;
+    }
+    base += tot;
+  }
+  for (int i = base + lane; i < QM; i += 32) out[i] = -1;
+  if (lane == 0) rcount[kv] = base;
+}
+
+// per-(b,h) stable descending argsort of the M counts (bitonic on 64-bit keys)
+__global__ void reverse_sort_kernel(const int32_t* __restrict__ rcount, int M, int Mp,
+                                    int32_t* __restrict__ sorted_kv) {
+  extern __shared__ unsigned long long rs_keys[];
+  const int tid = threadIdx.x;
+  const int64_t bh = blockIdx.x;
+  for (int j = tid; j < Mp; j += blockDim.x) {
+    unsigned long long key = 0ull;
+    if (j < M)
+      key = (static_cast<unsigned long long>(static_cast<unsigned>(rcount[bh * M + j]) + 1u) << 32) |
+            static_cast<unsigned long long>(0xffffffffu - static_cast<unsigned>(j));
+    rs_keys[j] = key;
+  }
+  __syncthreads();
+  for (int k = 2; k <= Mp; k <<= 1) {
+    for (int s = k >> 1; s > 0; s >>= 1) {
+      for (int i = tid; i < Mp; i += blockDim.x) {
+        const int p = i ^ s;
+        if (p > i) {
+          const unsigned long long a = rs_keys[i], b = rs_keys[p];
+          const bool desc = ((i & k) == 0);
+          if (desc ? (a < b) : (a > b)) { rs_keys[i] = b; rs_keys[p] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (int r = tid; r < M; r += blockDim.x)
+    sorted_kv[bh * M + r] =
+        static_cast<int>(0xffffffffu - static_cast<unsigned>(rs_keys[r] & 0xffffffffull));
+}
+
+// ------------------------------------------------------------ count sort
+// Replaces sort_by_count_launch (flash_topk_attn_v2/csrc/sort_by_count_kernel.cu:12-52,
+// a CUB device radix sort): stable counting sort, descending.  Chunks of the
+// input are histogrammed, a single CTA turns the [key][chunk] table into start
+// offsets (key descending, chunk ascending), and each chunk is then placed by
+// one warp walking it in order so equal counts keep ascending flat id.
+constexpr int SBC_CHUNK = 2048;
+
+__global__ void sbc_hist_kernel(const int32_t* __restrict__ counts, int64_t total, int range,
+                                int nchunk, unsigned* __restrict__ table) {
+  const int chunk = blockIdx.x;
+  const int64_t b0 = static_cast<int64_t>(chunk) * SBC_CHUNK;
+  const int64_t b1 = min(static_cast<long long>(total), static_cast<long long>(b0) + SBC_CHUNK);
+  for (int64_t i = b0 + threadIdx.x; i < b1; i += blockDim.x) {
+    int key = counts[i];
+    key = min(max(key, 0), range - 1);
+    atomicAdd(&table[static_cast<size_t>(key) * nchunk + chunk], 1u);
+  }
+}
+// exclusive scan of the table read in (key descending, chunk ascending) order
+constexpr int SBC_SCAN_THREADS = 512;
+__global__ void __launch_bounds__(SBC_SCAN_THREADS)
+sbc_scan_kernel(unsigned* __restrict__ table, int range, int nchunk) {
+  __shared__ unsigned warp_tot[SBC_SCAN_THREADS / 32];
+  __shared__ unsigned carry_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) carry_s = 0;
+  __syncthreads();
+  const int64_t n = static_cast<int64_t>(range) * nchunk;
+  for (int64_t b = 0; b < n; b += SBC_SCAN_THREADS) {
+    const int64_t i = b + tid;
+    int64_t src = 0;
+    unsigned v = 0;
+    if (i < n) {
+      const int64_t key = range - 1 - i / nchunk, chunk = i % nchunk;
+      src = key * nchunk + chunk;
+      v = table[src];
+    }
+    unsigned inc = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const unsigned u = __shfl_up_sync(0xffffffffu, inc, d);
+      if (lane >= d) inc += u;
+    }
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    unsigned woff = 0, btot = 0;
+    for (int wv = 0; wv < SBC_SCAN_THREADS / 32; wv++) {
+      const unsigned t = warp_tot[wv];
+      if (wv < warp) woff += t;
+      btot += t;
+    }
+    const unsigned carry = carry_s;
+    if (i < n) table[src] = carry + woff + inc - v;
+    __syncthreads();
+    if (tid == 0) carry_s = carry + btot;
+    __syncthreads();
+  }
+}
+__global__ void sbc_place_kernel(const int32_t* __restrict__ counts, int64_t total, int range,
+                                 int nchunk, unsigned* __restrict__ table,
+                                 int32_t* __restrict__ sorted_counts,
+                                 int32_t* __restrict__ sorted_ids) {
+  const int chunk = blockIdx.x;
+  const int lane = threadIdx.x;
+  const int64_t b0 = static_cast<int64_t>(chunk) * SBC_CHUNK;
+  const int64_t b1 = min(static_cast<long long>(total), static_cast<long long>(b0) + SBC_CHUNK);
+  for (int64_t i0 = b0; i0 < b1; i0 += 32) {
+    const int64_t i = i0 + lane;
+    const bool act = i < b1;
+    int raw = act ? counts[i] : 0;
+    int key = act ? min(max(raw, 0), range - 1) : -1 - lane;
+    const unsigned grp = __match_any_sync(0xffffffffu, key);
+    const int rank = __popc(grp & ((1u << lane) - 1u));
+    unsigned base = 0;
+    if (act) base = table[static_cast<size_t>(key) * nchunk + chunk];
+    __syncwarp();
+    if (act) {
+      sorted_counts[base + rank] = raw;
+      sorted_ids[base + rank] = static_cast<int32_t>(i);
+      if (rank == __popc(grp) - 1) table[static_cast<size_t>(key) * nchunk + chunk] = base + rank + 1;
+    }
+    __syncwarp();
+  }
+}
+
+}  // namespace ftk
+
+using namespace ftk;
+
+extern "C" int ftk_topk_select(const float* block_scores, const float* row_scale, int64_t rows,
+                               int M, int max_topk, int score_block_size, int pad_head,
+                               int pad_tail, float threshold, int32_t* topk_idx, float* topk_raw,
+                               float* topk_avg, int32_t* status, void* stream) {
+  (void)status;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return select_launch(block_scores, row_scale, rows, M, max_topk, score_block_size, pad_head,
+                       pad_tail, threshold, topk_idx, topk_raw, topk_avg, st);
+}
+
+static int next_pow2(int v) {
+  int p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+extern "C" int ftk_qblock_merge(const int32_t* topk_idx, const float* topk_scores, int64_t BH,
+                                int64_t N, int K, int q_block_size, int q_pad_head,
+                                int q_pad_tail, int num_score_blocks, int qblock_topk,
+                                int32_t* merged_idx, float* merged_scores, int32_t* counts,
+                                int32_t* status, void* stream) {
+  if (!topk_idx || !merged_idx || BH <= 0 || N <= 0 || K <= 0) return FTK_ERR_BAD_ARG;
+  if (q_block_size <= 0 || qblock_topk <= 0 || num_score_blocks <= 0) return FTK_ERR_BAD_ARG;
+  if (q_pad_head < 0 || q_pad_tail < 0 || q_pad_head >= q_block_size ||
+      q_pad_tail >= q_block_size)
+    return FTK_ERR_BAD_ARG;
+  if ((q_pad_head + N + q_pad_tail) % q_block_size != 0) return FTK_ERR_BAD_ARG;
+  if (num_score_blocks > 4096) return FTK_ERR_UNSUPPORTED;
+  const int64_t QM = (q_pad_head + N + q_pad_tail) / q_block_size;
+  if (BH * QM > 0x7fffffffLL || QM > 0x7fffffffLL) return FTK_ERR_BAD_ARG;
+  const int Mp = std::max(32, next_pow2(num_score_blocks));
+  const size_t smem = static_cast<size_t>(Mp) * 12;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(qblock_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return FTK_ERR_CUDA;
+  qblock_merge_kernel<<<static_cast<unsigned>(BH * QM), MG_THREADS, smem, st>>>(
+      topk_idx, topk_scores, N, K, q_block_size, q_pad_head, static_cast<int>(QM),
+      num_score_blocks, Mp, qblock_topk, merged_idx, merged_scores, counts, status);
+  return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+}
+
+extern "C" int ftk_max_index_plus1(const int32_t* idx, int64_t count, int32_t* result,
+                                   void* stream) {
+  if (!idx || !result || count < 0) return FTK_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  set_one_kernel<<<1, 1, 0, st>>>(result);
+  if (count > 0) {
+    const int grid = static_cast<int>(std::min<int64_t>((count + 255) / 256, 148 * 8));
+    max_index_kernel<<<grid, 256, 0, st>>>(idx, count, result);
+  }
+  return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+}
+
+extern "C" size_t ftk_build_reverse_workspace(int64_t BH, int QM, int M) {
+  const size_t words = static_cast<size_t>((QM + 31) / 32);
+  return ((static_cast<size_t>(BH) * M * words * 4) + 255) & ~static_cast<size_t>(255);
+}
+
+extern "C" int ftk_build_reverse(const int32_t* merged_idx, const int32_t* counts, int64_t BH,
+                                 int QM, int W, int M, int32_t* reverse_idx,
+                                 int32_t* reverse_counts, int32_t* sorted_kv, void* workspace,
+                                 size_t workspace_bytes, int32_t* status, void* stream) {
+  if (!merged_idx || !reverse_idx || !reverse_counts) return FTK_ERR_BAD_ARG;
+  if (BH <= 0 || QM <= 0 || W <= 0 || M <= 0) return FTK_ERR_BAD_ARG;
+  if (sorted_kv && M > 8192) return FTK_ERR_UNSUPPORTED;
+  if (!workspace || workspace_bytes < ftk_build_reverse_workspace(BH, QM, M))
+    return FTK_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int words = (QM + 31) / 32;
+  unsigned* bits = static_cast<unsigned*>(workspace);
+  if (cudaMemsetAsync(bits, 0, static_cast<size_t>(BH) * M * words * 4, st) != cudaSuccess)
+    return FTK_ERR_CUDA;
+  const int64_t total_qb = BH * QM, total_kv = BH * M;
+  reverse_mark_kernel<<<static_cast<unsigned>((total_qb * 32 + 255) / 256), 256, 0, st>>>(
+      merged_idx, counts, total_qb, QM, W, M, words, bits, status);
+  reverse_list_kernel<<<static_cast<unsigned>((total_kv * 32 + 255) / 256), 256, 0, st>>>(
+      bits, total_kv, QM, words, reverse_idx, reverse_counts);
+  if (sorted_kv) {
+    const int Mp = std::max(32, next_pow2(M));
+    const size_t smem = static_cast<size_t>(Mp) * 8;
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(reverse_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return FTK_ERR_CUDA;
+    reverse_sort_kernel<<<static_cast<unsigned>(BH), 256, smem, st>>>(reverse_counts, M, Mp,
+                                                                     sorted_kv);
+  }
+  return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+}
+
+extern "C" size_t ftk_sort_by_count_workspace(int64_t total, int max_count) {
+  const size_t nchunk = static_cast<size_t>((total + SBC_CHUNK - 1) / SBC_CHUNK);
+  return ((static_cast<size_t>(max_count) + 1) * nchunk * 4 + 255) & ~static_cast<size_t>(255);
+}
+
+extern "C" int ftk_sort_by_count(const int32_t* counts, int64_t total, int max_count,
+                                 int32_t* sorted_counts, int32_t* sorted_ids, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+  if (!counts || !sorted_counts || !sorted_ids || total <= 0 || max_count < 0)
+    return FTK_ERR_BAD_ARG;
+  if (total > 0x7fffffffLL) return FTK_ERR_UNSUPPORTED;
+  if (!workspace || workspace_bytes < ftk_sort_by_count_workspace(total, max_count))
+    return FTK_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int range = max_count + 1;
+  const int nchunk = static_cast<int>((total + SBC_CHUNK - 1) / SBC_CHUNK);
+  unsigned* table = static_cast<unsigned*>(workspace);
+  if (cudaMemsetAsync(table, 0, static_cast<size_t>(range) * nchunk * 4, st) != cudaSuccess)
+    return FTK_ERR_CUDA;
+  sbc_hist_kernel<<<nchunk, 256, 0, st>>>(counts, total, range, nchunk, table);
+  sbc_scan_kernel<<<1, SBC_SCAN_THREADS, 0, st>>>(table, range, nchunk);
+  sbc_place_kernel<<<nchunk, 32, 0, st>>>(counts, total, range, nchunk, table, sorted_counts,
+                                          sorted_ids);
+  return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+}

@@ -1,0 +1,712 @@
+// Sparse-attention backward for sm_100a: delta, dQ and dK/dV.
+//
+// Replaces preprocess_delta (flash_topk_attn_v2/sparse_attn_bwd.py:12-33),
+// sparse_attn_bwd_dq_kernel (csrc/sparse_attn_bwd_dq_kernel.cu:6-419) and
+// sparse_attn_bwd_dkv_sorted_kernel (csrc/sparse_attn_bwd_dkv_kernel.cu:6-435).
+//
+// Both kernels use the 128-row union tiles of attn_common.cuh and the same
+// three roles as the forward (TMA producer warp, UMMA issuer warp, 128 compute
+// threads owning one TMEM lane each).  With P = 2^(c S - lse2):
+//   dQ  kernel, per candidate KV block:  S = Q K^T, dP = dO V^T  (SS UMMAs),
+//        dS = P (dP - delta) rounded to the I/O dtype in TMEM, dQ += dS K
+//        (A from TMEM, K read MN-major from the tile that fed S).
+//   dKV kernel, per q-block of the reverse list: S^T = K Q^T, dP^T = V dO^T,
+//        P^T and dS^T written over the S^T / dP^T columns they came from,
+//        dV += P^T dO, dK += dS^T Q (dO, Q read MN-major).  One CTA owns its
+//        128 kv rows, so dK/dV need no atomics.
+#include <algorithm>
+#include <cmath>
+
+#include "attn_common.cuh"
+#include "ftk_host.cuh"
+#include "ftk_sm100.cuh"
+
+namespace ftk {
+
+// ------------------------------------------------------------------- delta
+// delta[bh][n] = sum_d o * do, one warp per (b, n, h) row.
+__global__ void delta_kernel(const uint8_t* __restrict__ o, const uint8_t* __restrict__ dout,
+                             int fmt, int64_t B, int64_t N, int64_t H, int D, int64_t so_b,
+                             int64_t so_n, int64_t so_h, int64_t sd_b, int64_t sd_n, int64_t sd_h,
+                             float* __restrict__ delta) {
+  const int64_t row = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= B * N * H) return;
+  const int64_t h = row % H, n = (row / H) % N, b = row / (H * N);
+  const uint32_t* po = reinterpret_cast<const uint32_t*>(o + 2 * (b * so_b + n * so_n + h * so_h));
+  const uint32_t* pd =
+      reinterpret_cast<const uint32_t*>(dout + 2 * (b * sd_b + n * sd_n + h * sd_h));
+  float acc = 0.f;
+  for (int i = lane; i < D / 2; i += 32) {
+    const float2 a = unpack2(po[i], fmt), g = unpack2(pd[i], fmt);
+    acc = fmaf(a.x, g.x, acc);
+    acc = fmaf(a.y, g.y, acc);
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+  if (lane == 0) delta[(b * H + h) * N + n] = acc;
+}
+
+constexpr int BW_THREADS = 192;
+constexpr int BW_MAX_STAGES = 4;
+
+struct BwdParams {
+  int N, H, QM, W, Mkv;
+  int g, kvb, q_pad_head, kv_pad_head;
+  int G, fmt, nstages;
+  float scale, scale_log2;
+  const int32_t* lists;      // dQ: merged [BH][QM][W]; dKV: reverse_idx [BH][Mkv][QM]
+  const int32_t* counts;     // dKV: reverse_counts [BH][Mkv]
+  const float* lse;
+  const float* delta;
+  void* out0;                // dQ kernel: dq ; dKV kernel: dk
+  void* out1;                //                  dKV kernel: dv
+  int64_t s0_b, s0_n, s0_h, s1_b, s1_n, s1_h;
+  int* status;
+};
+
+// ---------------------------------------------------------------------- dQ
+// TMEM columns: S[2] 0/64, dP[2] 128/192, dS[2] 256/288 (packed), dQ 384..
+template <int D>
+__global__ void __launch_bounds__(BW_THREADS, 1)
+sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
+                     const __grid_constant__ CUtensorMap tm_do,
+                     const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, const BwdParams p) {
+  constexpr int NCH = D / 64;
+  constexpr int ROW_TILE_BYTES = NCH * 128 * 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = smem + ROW_TILE_BYTES;
+  uint8_t* sKV = smem + 2 * ROW_TILE_BYTES;
+  __shared__ UnionScratch un;
+  __shared__ __align__(8) uint64_t bars[1 + 2 * BW_MAX_STAGES + 6];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m0 = blockIdx.x * p.G;
+  const int bh = blockIdx.y;
+  const int b_idx = bh / p.H, h_idx = bh - b_idx * p.H;
+  const int groups = min(p.G, p.QM - m0);
+  const int tile_row0 = m0 * p.g - p.q_pad_head;
+  const int kv_chunk_bytes = p.kvb * 128;
+  const int stage_bytes = 2 * NCH * kv_chunk_bytes;
+  const int NST = p.nstages;
+
+  const uint32_t bar_q = smem_u32(&bars[0]);
+  auto bar_kvfull = [&](int s) { return smem_u32(&bars[1 + s]); };
+  auto bar_kvempty = [&](int s) { return smem_u32(&bars[1 + BW_MAX_STAGES + s]); };
+  auto bar_afull = [&](int s) { return smem_u32(&bars[1 + 2 * BW_MAX_STAGES + s]); };
+  auto bar_dsfull = [&](int s) { return smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 2 + s]); };
+  auto bar_bdone = [&](int s) { return smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 4 + s]); };
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(bar_q, 1);
+    for (int s = 0; s < BW_MAX_STAGES; s++) {
+      mbar_init(bar_kvfull(s), 1);
+      mbar_init(bar_kvempty(s), 1);
+    }
+    for (int s = 0; s < 2; s++) {
+      mbar_init(bar_afull(s), 1);
+      mbar_init(bar_dsfull(s), 4);
+      mbar_init(bar_bdone(s), 1);
+    }
+    mbar_init_fence();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_do);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_base_s), 512);
+    tmem_relinquish();
+  }
+  const int n = build_union(un, p.lists + (static_cast<int64_t>(bh) * p.QM + m0) * p.W, p.W,
+                            groups, p.W, nullptr, p.Mkv, p.status);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  WaitCtx w{&abort_flag, p.status};
+
+  if (warp == 0) {
+    if (lane == 0 && n > 0) {
+      mbar_expect_tx(bar_q, 2 * ROW_TILE_BYTES);
+      for (int c = 0; c < NCH; c++) {
+        tma_load_4d(smem_u32(sQ) + c * 128 * 128, &tm_q, bar_q, c * 64, h_idx, tile_row0, b_idx);
+        tma_load_4d(smem_u32(sDO) + c * 128 * 128, &tm_do, bar_q, c * 64, h_idx, tile_row0, b_idx);
+      }
+      for (int i = 0; i < n; i++) {
+        const int s = i % NST;
+        if (!mbar_wait(bar_kvempty(s), ((i / NST) & 1) ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
+        const int tok0 = static_cast<int>(un.ids[i]) * p.kvb - p.kv_pad_head;
+        const uint32_t base = smem_u32(sKV) + s * stage_bytes;
+        mbar_expect_tx(bar_kvfull(s), stage_bytes);
+        for (int c = 0; c < NCH; c++) {
+          tma_load_4d(base + c * kv_chunk_bytes, &tm_k, bar_kvfull(s), c * 64, h_idx, tok0, b_idx);
+          tma_load_4d(base + (NCH + c) * kv_chunk_bytes, &tm_v, bar_kvfull(s), c * 64, h_idx, tok0,
+                      b_idx);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n > 0) {
+      const uint32_t idesc_a = umma_idesc(128, p.kvb, p.fmt, 0, 0);
+      const uint32_t idesc_b = umma_idesc(128, D, p.fmt, 0, 1);
+      bool ok = mbar_wait(bar_q, 0, w, FTK_DEV_TIMEOUT_MMA);
+      auto issue_a = [&](int i) -> bool {
+        const int s = i % NST;
+        if (!mbar_wait(bar_kvfull(s), (i / NST) & 1, w, FTK_DEV_TIMEOUT_MMA)) return false;
+        tc_fence_after();
+        const uint32_t kbase = smem_u32(sKV) + s * stage_bytes;
+        const uint32_t vbase = kbase + NCH * kv_chunk_bytes;
+        const uint32_t sb = i & 1;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ks++) {
+          const uint32_t qoff = (ks / 4) * 128 * 128 + (ks % 4) * 32;
+          const uint32_t koff = (ks / 4) * kv_chunk_bytes + (ks % 4) * 32;
+          umma_ss(tmem + sb * 64, smem_desc_sw128(smem_u32(sQ) + qoff, 16, 1024),
+                  smem_desc_sw128(kbase + koff, 16, 1024), idesc_a, ks > 0);
+        }
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ks++) {
+          const uint32_t qoff = (ks / 4) * 128 * 128 + (ks % 4) * 32;
+          const uint32_t koff = (ks / 4) * kv_chunk_bytes + (ks % 4) * 32;
+          umma_ss(tmem + 128 + sb * 64, smem_desc_sw128(smem_u32(sDO) + qoff, 16, 1024),
+                  smem_desc_sw128(vbase + koff, 16, 1024), idesc_a, ks > 0);
+        }
+        umma_commit(bar_afull(sb));
+        return true;
+      };
+      if (ok) ok = issue_a(0);
+      if (ok && n > 1) ok = issue_a(1);
+      for (int i = 0; ok && i < n; i++) {
+        const int s = i % NST, sb = i & 1;
+        if (!mbar_wait(bar_dsfull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t kbase = smem_u32(sKV) + s * stage_bytes;
+        for (int ks = 0; ks < p.kvb / 16; ks++)
+          umma_ts(tmem + 384, tmem + 256 + sb * 32 + ks * 8,
+                  smem_desc_sw128(kbase + ks * 2048, kv_chunk_bytes, 1024), idesc_b,
+                  (i > 0) || (ks > 0));
+        umma_commit(bar_bdone(sb));
+        umma_commit(bar_kvempty(s));
+        if (i + 2 < n) ok = issue_a(i + 2);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int grp = r / p.g;
+    const int qrow = tile_row0 + r;
+    const bool row_valid = (grp < groups) && qrow >= 0 && qrow < p.N;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    const float c = p.scale_log2;
+    float lse2 = 0.f, dl = 0.f;
+    if (row_valid) {
+      lse2 = p.lse[static_cast<int64_t>(bh) * p.N + qrow] * 1.4426950408889634f;
+      dl = p.delta[static_cast<int64_t>(bh) * p.N + qrow];
+    }
+    bool ok = true;
+    for (int i = 0; ok && i < n; i++) {
+      const int sb = i & 1;
+      if (!mbar_wait(bar_afull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) { ok = false; break; }
+      if (i >= 2 && !mbar_wait(bar_bdone(sb), ((i - 2) >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int tok0 = static_cast<int>(un.ids[i]) * p.kvb - p.kv_pad_head;
+      const int lo = max(0, -tok0), hi = min(p.kvb, p.N - tok0);
+      const bool act = row_valid && ((un.masks[i] >> grp) & 1) && hi > lo;
+      for (int c0 = 0; c0 < p.kvb; c0 += 16) {
+        uint32_t sv[16], dv[16], pk[8];
+        tmem_ld16(lane_addr + sb * 64 + c0, sv);
+        tmem_ld16(lane_addr + 128 + sb * 64 + c0, dv);
+        tmem_wait_ld();
+#pragma unroll
+        for (int x = 0; x < 16; x += 2) {
+          float d0 = 0.f, d1 = 0.f;
+          if (act && c0 + x >= lo && c0 + x < hi) {
+            const float pr = fast_exp2(fmaf(__uint_as_float(sv[x]), c, -lse2));
+            d0 = pr * (__uint_as_float(dv[x]) - dl);
+          }
+          if (act && c0 + x + 1 >= lo && c0 + x + 1 < hi) {
+            const float pr = fast_exp2(fmaf(__uint_as_float(sv[x + 1]), c, -lse2));
+            d1 = pr * (__uint_as_float(dv[x + 1]) - dl);
+          }
+          pk[x >> 1] = pack2(d0, d1, p.fmt);
+        }
+        tmem_st8(lane_addr + 256 + sb * 32 + (c0 >> 1), pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_dsfull(sb));
+    }
+    if (ok && n > 0)
+      ok = mbar_wait(bar_bdone((n - 1) & 1), ((n - 1) >> 1) & 1, w, FTK_DEV_TIMEOUT_EPILOGUE);
+    if (ok) {
+      tc_fence_after();
+      uint8_t* orow = nullptr;
+      if (row_valid)
+        orow = static_cast<uint8_t*>(p.out0) +
+               2 * (static_cast<int64_t>(b_idx) * p.s0_b + static_cast<int64_t>(qrow) * p.s0_n +
+                    static_cast<int64_t>(h_idx) * p.s0_h);
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t v[32];
+        if (n > 0) {
+          tmem_ld32(lane_addr + 384 + c0, v);
+          tmem_wait_ld();
+        }
+        if (row_valid) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int x = 0; x < 32; x += 2) {
+            const float a = n > 0 ? __uint_as_float(v[x]) * p.scale : 0.f;
+            const float b = n > 0 ? __uint_as_float(v[x + 1]) * p.scale : 0.f;
+            pk[x >> 1] = pack2(a, b, p.fmt);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(orow + c0 * 2);
+#pragma unroll
+          for (int x = 0; x < 4; x++)
+            dst[x] = make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag)
+    for (int i = 0; i < 200; i++) __nanosleep(1000);
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// -------------------------------------------------------------------- dK/dV
+// TMEM columns: S^T[2] 0/64 (P^T written over their first half), dP^T[2]
+// 128/192 (dS^T likewise), dV 256.., dK 384..
+template <int D>
+__global__ void __launch_bounds__(BW_THREADS, 1)
+sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
+                      const __grid_constant__ CUtensorMap tm_do,
+                      const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_v, const BwdParams p) {
+  constexpr int NCH = D / 64;
+  constexpr int ROW_TILE_BYTES = NCH * 128 * 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + ROW_TILE_BYTES;
+  uint8_t* sQD = smem + 2 * ROW_TILE_BYTES;
+  __shared__ UnionScratch un;
+  __shared__ __align__(8) uint64_t bars[1 + 2 * BW_MAX_STAGES + 6];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  __shared__ float s_lse2[2][128], s_delta[2][128];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int j0 = blockIdx.x * p.G;          // first kv block of the tile
+  const int bh = blockIdx.y;
+  const int b_idx = bh / p.H, h_idx = bh - b_idx * p.H;
+  const int groups = min(p.G, p.Mkv - j0);
+  const int tile_tok0 = j0 * p.kvb - p.kv_pad_head;
+  const int q_chunk_bytes = p.g * 128;
+  const int stage_bytes = 2 * NCH * q_chunk_bytes;
+  const int NST = p.nstages;
+
+  const uint32_t bar_kv = smem_u32(&bars[0]);
+  auto bar_qfull = [&](int s) { return smem_u32(&bars[1 + s]); };
+  auto bar_qempty = [&](int s) { return smem_u32(&bars[1 + BW_MAX_STAGES + s]); };
+  auto bar_afull = [&](int s) { return smem_u32(&bars[1 + 2 * BW_MAX_STAGES + s]); };
+  auto bar_pfull = [&](int s) { return smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 2 + s]); };
+  auto bar_bdone = [&](int s) { return smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 4 + s]); };
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(bar_kv, 1);
+    for (int s = 0; s < BW_MAX_STAGES; s++) {
+      mbar_init(bar_qfull(s), 1);
+      mbar_init(bar_qempty(s), 1);
+    }
+    for (int s = 0; s < 2; s++) {
+      mbar_init(bar_afull(s), 1);
+      mbar_init(bar_pfull(s), 4);
+      mbar_init(bar_bdone(s), 1);
+    }
+    mbar_init_fence();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_do);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_base_s), 512);
+    tmem_relinquish();
+  }
+  const int64_t kv_row = static_cast<int64_t>(bh) * p.Mkv + j0;
+  const int n = build_union(un, p.lists + kv_row * p.QM, p.QM, groups, p.QM, p.counts + kv_row,
+                            p.QM, p.status);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  WaitCtx w{&abort_flag, p.status};
+
+  if (warp == 0) {
+    if (lane == 0 && n > 0) {
+      mbar_expect_tx(bar_kv, 2 * ROW_TILE_BYTES);
+      for (int c = 0; c < NCH; c++) {
+        tma_load_4d(smem_u32(sK) + c * 128 * 128, &tm_k, bar_kv, c * 64, h_idx, tile_tok0, b_idx);
+        tma_load_4d(smem_u32(sV) + c * 128 * 128, &tm_v, bar_kv, c * 64, h_idx, tile_tok0, b_idx);
+      }
+      for (int i = 0; i < n; i++) {
+        const int s = i % NST;
+        if (!mbar_wait(bar_qempty(s), ((i / NST) & 1) ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
+        const int row0 = static_cast<int>(un.ids[i]) * p.g - p.q_pad_head;
+        const uint32_t base = smem_u32(sQD) + s * stage_bytes;
+        mbar_expect_tx(bar_qfull(s), stage_bytes);
+        for (int c = 0; c < NCH; c++) {
+          tma_load_4d(base + c * q_chunk_bytes, &tm_q, bar_qfull(s), c * 64, h_idx, row0, b_idx);
+          tma_load_4d(base + (NCH + c) * q_chunk_bytes, &tm_do, bar_qfull(s), c * 64, h_idx, row0,
+                      b_idx);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n > 0) {
+      const uint32_t idesc_a = umma_idesc(128, p.g, p.fmt, 0, 0);
+      const uint32_t idesc_b = umma_idesc(128, D, p.fmt, 0, 1);
+      bool ok = mbar_wait(bar_kv, 0, w, FTK_DEV_TIMEOUT_MMA);
+      auto issue_a = [&](int i) -> bool {
+        const int s = i % NST;
+        if (!mbar_wait(bar_qfull(s), (i / NST) & 1, w, FTK_DEV_TIMEOUT_MMA)) return false;
+        tc_fence_after();
+        const uint32_t qbase = smem_u32(sQD) + s * stage_bytes;
+        const uint32_t dobase = qbase + NCH * q_chunk_bytes;
+        const uint32_t sb = i & 1;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ks++) {
+          const uint32_t aoff = (ks / 4) * 128 * 128 + (ks % 4) * 32;
+          const uint32_t boff = (ks / 4) * q_chunk_bytes + (ks % 4) * 32;
+          umma_ss(tmem + sb * 64, smem_desc_sw128(smem_u32(sK) + aoff, 16, 1024),
+                  smem_desc_sw128(qbase + boff, 16, 1024), idesc_a, ks > 0);
+        }
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ks++) {
+          const uint32_t aoff = (ks / 4) * 128 * 128 + (ks % 4) * 32;
+          const uint32_t boff = (ks / 4) * q_chunk_bytes + (ks % 4) * 32;
+          umma_ss(tmem + 128 + sb * 64, smem_desc_sw128(smem_u32(sV) + aoff, 16, 1024),
+                  smem_desc_sw128(dobase + boff, 16, 1024), idesc_a, ks > 0);
+        }
+        umma_commit(bar_afull(sb));
+        return true;
+      };
+      if (ok) ok = issue_a(0);
+      if (ok && n > 1) ok = issue_a(1);
+      for (int i = 0; ok && i < n; i++) {
+        const int s = i % NST, sb = i & 1;
+        if (!mbar_wait(bar_pfull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t qbase = smem_u32(sQD) + s * stage_bytes;
+        const uint32_t dobase = qbase + NCH * q_chunk_bytes;
+        for (int ks = 0; ks < p.g / 16; ks++) {
+          const bool acc = (i > 0) || (ks > 0);
+          umma_ts(tmem + 256, tmem + sb * 64 + ks * 8,
+                  smem_desc_sw128(dobase + ks * 2048, q_chunk_bytes, 1024), idesc_b, acc);
+          umma_ts(tmem + 384, tmem + 128 + sb * 64 + ks * 8,
+                  smem_desc_sw128(qbase + ks * 2048, q_chunk_bytes, 1024), idesc_b, acc);
+        }
+        umma_commit(bar_bdone(sb));
+        umma_commit(bar_qempty(s));
+        if (i + 2 < n) ok = issue_a(i + 2);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int ct = tid - 64;                 // 0..127 among the compute threads
+    const int grp = r / p.kvb;
+    const int tok = tile_tok0 + r;
+    const bool row_valid = (grp < groups) && tok >= 0 && tok < p.N;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    const float c = p.scale_log2;
+    bool ok = true;
+    // every compute thread runs all n rounds (the named barrier below needs
+    // all 128 of them); after a failed wait a thread only keeps the barrier
+    // company and does no more work.
+    for (int i = 0; i < n; i++) {
+      const int sb = i & 1;
+      const int row0 = static_cast<int>(un.ids[i]) * p.g - p.q_pad_head;
+      if (ct < p.g) {
+        const int t = row0 + ct;
+        float l2 = 0.f, dl = 0.f;
+        if (t >= 0 && t < p.N) {
+          l2 = p.lse[static_cast<int64_t>(bh) * p.N + t] * 1.4426950408889634f;
+          dl = p.delta[static_cast<int64_t>(bh) * p.N + t];
+        }
+        s_lse2[sb][ct] = l2;
+        s_delta[sb][ct] = dl;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!ok) continue;
+      if (!mbar_wait(bar_afull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) {
+        ok = false;
+        continue;
+      }
+      tc_fence_after();
+      const int lo = max(0, -row0), hi = min(p.g, p.N - row0);
+      const bool act = row_valid && ((un.masks[i] >> grp) & 1) && hi > lo;
+      for (int c0 = 0; c0 < p.g; c0 += 16) {
+        uint32_t sv[16], dv[16], pp[8], pd[8];
+        tmem_ld16(lane_addr + sb * 64 + c0, sv);
+        tmem_ld16(lane_addr + 128 + sb * 64 + c0, dv);
+        tmem_wait_ld();
+#pragma unroll
+        for (int x = 0; x < 16; x += 2) {
+          float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
+          if (act && c0 + x >= lo && c0 + x < hi) {
+            p0 = fast_exp2(fmaf(__uint_as_float(sv[x]), c, -s_lse2[sb][c0 + x]));
+            d0 = p0 * (__uint_as_float(dv[x]) - s_delta[sb][c0 + x]);
+          }
+          if (act && c0 + x + 1 >= lo && c0 + x + 1 < hi) {
+            p1 = fast_exp2(fmaf(__uint_as_float(sv[x + 1]), c, -s_lse2[sb][c0 + x + 1]));
+            d1 = p1 * (__uint_as_float(dv[x + 1]) - s_delta[sb][c0 + x + 1]);
+          }
+          pp[x >> 1] = pack2(p0, p1, p.fmt);
+          pd[x >> 1] = pack2(d0, d1, p.fmt);
+        }
+        tmem_st8(lane_addr + sb * 64 + (c0 >> 1), pp);
+        tmem_st8(lane_addr + 128 + sb * 64 + (c0 >> 1), pd);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_pfull(sb));
+    }
+    if (ok && n > 0)
+      ok = mbar_wait(bar_bdone((n - 1) & 1), ((n - 1) >> 1) & 1, w, FTK_DEV_TIMEOUT_EPILOGUE);
+    if (ok) {
+      tc_fence_after();
+#pragma unroll
+      for (int which = 0; which < 2; which++) {
+        // which 0: dV (TMEM 256) -> out1 ; which 1: dK (TMEM 384, scaled) -> out0
+        uint8_t* base = static_cast<uint8_t*>(which == 0 ? p.out1 : p.out0);
+        const int64_t sb_ = which == 0 ? p.s1_b : p.s0_b, sn_ = which == 0 ? p.s1_n : p.s0_n,
+                      sh_ = which == 0 ? p.s1_h : p.s0_h;
+        const float mul = which == 0 ? 1.f : p.scale;
+        uint8_t* orow = nullptr;
+        if (row_valid)
+          orow = base + 2 * (static_cast<int64_t>(b_idx) * sb_ + static_cast<int64_t>(tok) * sn_ +
+                             static_cast<int64_t>(h_idx) * sh_);
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t v[32];
+          if (n > 0) {
+            tmem_ld32(lane_addr + 256 + which * 128 + c0, v);
+            tmem_wait_ld();
+          }
+          if (row_valid) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int x = 0; x < 32; x += 2) {
+              const float a = n > 0 ? __uint_as_float(v[x]) * mul : 0.f;
+              const float b = n > 0 ? __uint_as_float(v[x + 1]) * mul : 0.f;
+              pk[x >> 1] = pack2(a, b, p.fmt);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(orow + c0 * 2);
+#pragma unroll
+            for (int x = 0; x < 4; x++)
+              dst[x] = make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag)
+    for (int i = 0; i < 200; i++) __nanosleep(1000);
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+static int bwd_common_checks(int dtype, int64_t B, int64_t H, int64_t N, int64_t D, int QM, int g,
+                             int kvb, int q_pad_head, int kv_pad_head) {
+  if (B <= 0 || H <= 0 || N <= 0 || QM <= 0) return FTK_ERR_BAD_ARG;
+  if (dtype != FTK_DTYPE_F16 && dtype != FTK_DTYPE_BF16) return FTK_ERR_BAD_ARG;
+  if (g <= 0 || kvb <= 0) return FTK_ERR_BAD_ARG;
+  if (q_pad_head < 0 || q_pad_head >= g || kv_pad_head < 0 || kv_pad_head >= kvb)
+    return FTK_ERR_BAD_ARG;
+  if (static_cast<int64_t>(QM) * g < q_pad_head + N) return FTK_ERR_BAD_ARG;
+  if (D != 64 && D != 128) return FTK_ERR_UNSUPPORTED;
+  if (kvb % 16 != 0 || kvb > 64) return FTK_ERR_UNSUPPORTED;
+  if (B * H > 65535) return FTK_ERR_BAD_ARG;
+  return FTK_OK;
+}
+
+static bool aligned_out(const void* p, int64_t a, int64_t b, int64_t c) {
+  return p && !(reinterpret_cast<uintptr_t>(p) & 15u) && !(a & 7) && !(b & 7) && !(c & 7);
+}
+
+}  // namespace ftk
+
+using namespace ftk;
+
+extern "C" int ftk_sparse_bwd_dq(
+    const void* q, const void* k, const void* v, const void* o, const void* dout, int dtype,
+    int64_t B, int64_t H, int64_t N, int64_t D, int64_t sq_b, int64_t sq_n, int64_t sq_h,
+    int64_t sk_b, int64_t sk_n, int64_t sk_h, int64_t sv_b, int64_t sv_n, int64_t sv_h,
+    int64_t so_b, int64_t so_n, int64_t so_h, int64_t sdo_b, int64_t sdo_n, int64_t sdo_h,
+    const int32_t* merged_idx, int QM, int W, int q_block_size, int kv_block_size, int q_pad_head,
+    int kv_pad_head, float scale, const float* lse, float* delta, void* dq, int64_t sdq_b,
+    int64_t sdq_n, int64_t sdq_h, int32_t* status, void* stream) {
+  if (!q || !k || !v || !o || !dout || !merged_idx || !lse || !delta || W <= 0)
+    return FTK_ERR_BAD_ARG;
+  int e = bwd_common_checks(dtype, B, H, N, D, QM, q_block_size, kv_block_size, q_pad_head,
+                            kv_pad_head);
+  if (e) return e;
+  if (q_block_size > 128) return FTK_ERR_UNSUPPORTED;
+  if (!aligned_out(dq, sdq_b, sdq_n, sdq_h)) return FTK_ERR_BAD_ARG;
+  if ((so_b | so_n | so_h | sdo_b | sdo_n | sdo_h) & 1) return FTK_ERR_BAD_ARG;
+  const int64_t Mkv = (kv_pad_head + N + kv_block_size - 1) / kv_block_size;
+  if (Mkv > AT_MAX_BLOCKS) return FTK_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  const int64_t rows = B * N * H;
+  delta_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, st>>>(
+      static_cast<const uint8_t*>(o), static_cast<const uint8_t*>(dout), dtype, B, N, H,
+      static_cast<int>(D), so_b, so_n, so_h, sdo_b, sdo_n, sdo_h, delta);
+  if (cudaGetLastError() != cudaSuccess) return FTK_ERR_CUDA;
+
+  BwdParams p{};
+  p.N = static_cast<int>(N);
+  p.H = static_cast<int>(H);
+  p.QM = QM;
+  p.W = W;
+  p.Mkv = static_cast<int>(Mkv);
+  p.g = q_block_size;
+  p.kvb = kv_block_size;
+  p.q_pad_head = q_pad_head;
+  p.kv_pad_head = kv_pad_head;
+  p.G = std::max(1, std::min(AT_MAX_GROUPS, 128 / q_block_size));
+  p.fmt = dtype;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.lists = merged_idx;
+  p.lse = lse;
+  p.delta = delta;
+  p.out0 = dq;
+  p.s0_b = sdq_b;
+  p.s0_n = sdq_n;
+  p.s0_h = sdq_h;
+  p.status = status;
+
+  CUtensorMap tq, tdo, tk, tv;
+  if ((e = encode_tmap_bnhd(&tq, q, dtype, B, N, H, D, sq_b, sq_n, sq_h, 64, 128))) return e;
+  if ((e = encode_tmap_bnhd(&tdo, dout, dtype, B, N, H, D, sdo_b, sdo_n, sdo_h, 64, 128))) return e;
+  if ((e = encode_tmap_bnhd(&tk, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, kv_block_size)))
+    return e;
+  if ((e = encode_tmap_bnhd(&tv, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, kv_block_size)))
+    return e;
+  const int nch = static_cast<int>(D / 64);
+  const int stage_bytes = 2 * nch * kv_block_size * 128;
+  p.nstages = std::min(BW_MAX_STAGES, (128 * 1024) / stage_bytes);
+  if (p.nstages < 2) return FTK_ERR_UNSUPPORTED;
+  const size_t smem = 1024 + 2 * nch * 128 * 128 + static_cast<size_t>(p.nstages) * stage_bytes;
+  dim3 grid((QM + p.G - 1) / p.G, static_cast<unsigned>(B * H));
+  if (D == 64) {
+    if (cudaFuncSetAttribute(sparse_bwd_dq_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return FTK_ERR_CUDA;
+    sparse_bwd_dq_kernel<64><<<grid, BW_THREADS, smem, st>>>(tq, tdo, tk, tv, p);
+  } else {
+    if (cudaFuncSetAttribute(sparse_bwd_dq_kernel<128>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return FTK_ERR_CUDA;
+    sparse_bwd_dq_kernel<128><<<grid, BW_THREADS, smem, st>>>(tq, tdo, tk, tv, p);
+  }
+  return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+}
+
+extern "C" int ftk_sparse_bwd_dkv(
+    const void* q, const void* k, const void* v, const void* dout, int dtype, int64_t B, int64_t H,
+    int64_t N, int64_t D, int64_t sq_b, int64_t sq_n, int64_t sq_h, int64_t sk_b, int64_t sk_n,
+    int64_t sk_h, int64_t sv_b, int64_t sv_n, int64_t sv_h, int64_t sdo_b, int64_t sdo_n,
+    int64_t sdo_h, const int32_t* reverse_idx, const int32_t* reverse_counts,
+    const int32_t* sorted_kv, int QM, int M, int q_block_size, int kv_block_size, int q_pad_head,
+    int kv_pad_head, float scale, const float* lse, const float* delta, void* dk, int64_t sdk_b,
+    int64_t sdk_n, int64_t sdk_h, void* dv, int64_t sdv_b, int64_t sdv_n, int64_t sdv_h,
+    int32_t* status, void* stream) {
+  (void)sorted_kv;  // tiles are issued in block order; kept for interface parity
+  if (!q || !k || !v || !dout || !reverse_idx || !reverse_counts || !lse || !delta)
+    return FTK_ERR_BAD_ARG;
+  int e = bwd_common_checks(dtype, B, H, N, D, QM, q_block_size, kv_block_size, q_pad_head,
+                            kv_pad_head);
+  if (e) return e;
+  if (q_block_size % 16 != 0 || q_block_size > 64) return FTK_ERR_UNSUPPORTED;
+  if (QM > AT_MAX_BLOCKS) return FTK_ERR_UNSUPPORTED;
+  if (M <= 0 || static_cast<int64_t>(M) * kv_block_size < kv_pad_head + N) return FTK_ERR_BAD_ARG;
+  if (!aligned_out(dk, sdk_b, sdk_n, sdk_h) || !aligned_out(dv, sdv_b, sdv_n, sdv_h))
+    return FTK_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  BwdParams p{};
+  p.N = static_cast<int>(N);
+  p.H = static_cast<int>(H);
+  p.QM = QM;
+  p.W = QM;
+  p.Mkv = M;
+  p.g = q_block_size;
+  p.kvb = kv_block_size;
+  p.q_pad_head = q_pad_head;
+  p.kv_pad_head = kv_pad_head;
+  p.G = std::max(1, std::min(AT_MAX_GROUPS, 128 / kv_block_size));
+  p.fmt = dtype;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.lists = reverse_idx;
+  p.counts = reverse_counts;
+  p.lse = lse;
+  p.delta = delta;
+  p.out0 = dk;
+  p.s0_b = sdk_b;
+  p.s0_n = sdk_n;
+  p.s0_h = sdk_h;
+  p.out1 = dv;
+  p.s1_b = sdv_b;
+  p.s1_n = sdv_n;
+  p.s1_h = sdv_h;
+  p.status = status;
+
+  CUtensorMap tq, tdo, tk, tv;
+  if ((e = encode_tmap_bnhd(&tq, q, dtype, B, N, H, D, sq_b, sq_n, sq_h, 64, q_block_size)))
+    return e;
+  if ((e = encode_tmap_bnhd(&tdo, dout, dtype, B, N, H, D, sdo_b, sdo_n, sdo_h, 64, q_block_size)))
+    return e;
+  if ((e = encode_tmap_bnhd(&tk, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, 128))) return e;
+  if ((e = encode_tmap_bnhd(&tv, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, 128))) return e;
+  const int nch = static_cast<int>(D / 64);
+  const int stage_bytes = 2 * nch * q_block_size * 128;
+  p.nstages = std::min(BW_MAX_STAGES, (128 * 1024) / stage_bytes);
+  if (p.nstages < 2) return FTK_ERR_UNSUPPORTED;
+  const size_t smem = 1024 + 2 * nch * 128 * 128 + static_cast<size_t>(p.nstages) * stage_bytes;
+  dim3 grid((M + p.G - 1) / p.G, static_cast<unsigned>(B * H));
+  if (D == 64) {
+    if (cudaFuncSetAttribute(sparse_bwd_dkv_kernel<64>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return FTK_ERR_CUDA;
+    sparse_bwd_dkv_kernel<64><<<grid, BW_THREADS, smem, st>>>(tq, tdo, tk, tv, p);
+  } else {
+    if (cudaFuncSetAttribute(sparse_bwd_dkv_kernel<128>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return FTK_ERR_CUDA;
+    sparse_bwd_dkv_kernel<128><<<grid, BW_THREADS, smem, st>>>(tq, tdo, tk, tv, p);
+  }
+  return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+}

@@ -1,0 +1,379 @@
+// Gathered-KV flash attention forward for sm_100a.
+//
+// Replaces sparse_attn_fwd_kernel of the reference
+// (flash_topk_attn_v2/csrc/sparse_attn_kernel.cu:6-365).
+//
+// One CTA owns 128 consecutive virtual query rows = G q-blocks of one (batch,
+// head) slice and walks the union of their candidate KV blocks in ascending
+// order (see attn_common.cuh).  Roles: warp 0 = TMA producer (Q once, then a
+// ring of K/V block tiles), warp 1 = UMMA issuer, warps 2..5 = 128 softmax
+// threads, one query row each.
+//   S = Q K^T      tcgen05 SS, both operands K-major, accumulator in TMEM
+//   P = 2^(c S - m) rounded to the I/O dtype, written back to TMEM
+//   O += P V       tcgen05 with A = P from TMEM, B = V read MN-major from the
+//                  same row-major tile TMA delivered
+// S and P are double buffered so the tensor core computes S of block i+1 while
+// the softmax threads work on block i.  The running maximum is only raised
+// when a block exceeds it by more than 2^8 (P stays inside fp16 range); O is
+// then rescaled in TMEM by its row owner.
+#include <algorithm>
+#include <cmath>
+
+#include "attn_common.cuh"
+#include "ftk_host.cuh"
+#include "ftk_sm100.cuh"
+
+namespace ftk {
+
+constexpr int FW_THREADS = 192;
+constexpr int FW_MAX_STAGES = 4;
+constexpr int FW_COL_S = 0;      // S[2]: 2 x 128 columns
+constexpr int FW_COL_P = 256;    // P[2]: 2 x 64 columns (16-bit pairs)
+constexpr int FW_COL_O = 384;    // O: D columns
+
+struct FwdParams {
+  int N, H, QM, W, Mkv;
+  int g, kvb, q_pad_head, kv_pad_head;
+  int G, fmt, nstages;
+  float scale_log2;
+  const int32_t* merged;
+  void* o;
+  int64_t so_b, so_n, so_h;
+  float* lse;
+  int* status;
+};
+
+template <int D>
+__global__ void __launch_bounds__(FW_THREADS, 1)
+sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+  constexpr int NCH = D / 64;
+  constexpr int Q_BYTES = NCH * 128 * 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sKV = smem + Q_BYTES;
+  __shared__ UnionScratch un;
+  __shared__ __align__(8) uint64_t bars[1 + 2 * FW_MAX_STAGES + 6];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m0 = blockIdx.x * p.G;
+  const int bh = blockIdx.y;
+  const int b_idx = bh / p.H, h_idx = bh - b_idx * p.H;
+  const int groups = min(p.G, p.QM - m0);
+  const int tile_row0 = m0 * p.g - p.q_pad_head;
+  const int kv_chunk_bytes = p.kvb * 128;
+  const int stage_bytes = 2 * NCH * kv_chunk_bytes;
+  const int NST = p.nstages;
+
+  const uint32_t bar_q = smem_u32(&bars[0]);
+  auto bar_kvfull = [&](int s) { return smem_u32(&bars[1 + s]); };
+  auto bar_kvempty = [&](int s) { return smem_u32(&bars[1 + FW_MAX_STAGES + s]); };
+  auto bar_sfull = [&](int s) { return smem_u32(&bars[1 + 2 * FW_MAX_STAGES + s]); };
+  auto bar_pfull = [&](int s) { return smem_u32(&bars[1 + 2 * FW_MAX_STAGES + 2 + s]); };
+  auto bar_pvdone = [&](int s) { return smem_u32(&bars[1 + 2 * FW_MAX_STAGES + 4 + s]); };
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(bar_q, 1);
+    for (int s = 0; s < FW_MAX_STAGES; s++) {
+      mbar_init(bar_kvfull(s), 1);
+      mbar_init(bar_kvempty(s), 1);
+    }
+    for (int s = 0; s < 2; s++) {
+      mbar_init(bar_sfull(s), 1);
+      mbar_init(bar_pfull(s), 4);  // one arrival per softmax warp
+      mbar_init(bar_pvdone(s), 1);
+    }
+    mbar_init_fence();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_base_s), 512);
+    tmem_relinquish();
+  }
+  const int n = build_union(un, p.merged + (static_cast<int64_t>(bh) * p.QM + m0) * p.W, p.W,
+                            groups, p.W, nullptr, p.Mkv, p.status);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  WaitCtx w{&abort_flag, p.status};
+
+  if (warp == 0) {
+    // ------------------------------------------------------- TMA producer
+    if (lane == 0 && n > 0) {
+      mbar_expect_tx(bar_q, Q_BYTES);
+      for (int c = 0; c < NCH; c++)
+        tma_load_4d(smem_u32(sQ) + c * 128 * 128, &tm_q, bar_q, c * 64, h_idx, tile_row0, b_idx);
+      for (int i = 0; i < n; i++) {
+        const int s = i % NST;
+        const uint32_t ph = (i / NST) & 1;
+        if (!mbar_wait(bar_kvempty(s), ph ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
+        const int tok0 = static_cast<int>(un.ids[i]) * p.kvb - p.kv_pad_head;
+        const uint32_t base = smem_u32(sKV) + s * stage_bytes;
+        mbar_expect_tx(bar_kvfull(s), stage_bytes);
+        for (int c = 0; c < NCH; c++)
+          tma_load_4d(base + c * kv_chunk_bytes, &tm_k, bar_kvfull(s), c * 64, h_idx, tok0, b_idx);
+        for (int c = 0; c < NCH; c++)
+          tma_load_4d(base + (NCH + c) * kv_chunk_bytes, &tm_v, bar_kvfull(s), c * 64, h_idx, tok0,
+                      b_idx);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------- UMMA issuer
+    if (lane == 0 && n > 0) {
+      const uint32_t idesc_s = umma_idesc(128, p.kvb, p.fmt, 0, 0);
+      const uint32_t idesc_pv = umma_idesc(128, D, p.fmt, 0, 1);
+      bool ok = mbar_wait(bar_q, 0, w, FTK_DEV_TIMEOUT_MMA);
+      auto issue_s = [&](int i) -> bool {
+        const int s = i % NST;
+        if (!mbar_wait(bar_kvfull(s), (i / NST) & 1, w, FTK_DEV_TIMEOUT_MMA)) return false;
+        tc_fence_after();
+        const uint32_t kbase = smem_u32(sKV) + s * stage_bytes;
+        const uint32_t d_tmem = tmem + FW_COL_S + (i & 1) * 128;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ks++) {
+          umma_ss(d_tmem,
+                  smem_desc_sw128(smem_u32(sQ) + (ks / 4) * 128 * 128 + (ks % 4) * 32, 16, 1024),
+                  smem_desc_sw128(kbase + (ks / 4) * kv_chunk_bytes + (ks % 4) * 32, 16, 1024),
+                  idesc_s, ks > 0);
+        }
+        umma_commit(bar_sfull(i & 1));
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      if (ok && n > 1) ok = issue_s(1);
+      for (int i = 0; ok && i < n; i++) {
+        const int s = i % NST, sb = i & 1;
+        if (!mbar_wait(bar_pfull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t vbase = smem_u32(sKV) + s * stage_bytes + NCH * kv_chunk_bytes;
+        const int ksteps = p.kvb / 16;
+        for (int ks = 0; ks < ksteps; ks++) {
+          umma_ts(tmem + FW_COL_O, tmem + FW_COL_P + sb * 64 + ks * 8,
+                  smem_desc_sw128(vbase + ks * 2048, kv_chunk_bytes, 1024), idesc_pv,
+                  (i > 0) || (ks > 0));
+        }
+        umma_commit(bar_pvdone(sb));
+        umma_commit(bar_kvempty(s));
+        if (i + 2 < n) ok = issue_s(i + 2);
+      }
+    }
+  } else {
+    // ---------------------------------------------------- softmax threads
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int grp = r / p.g;
+    const int qrow = tile_row0 + r;
+    const bool row_valid = (grp < groups) && qrow >= 0 && qrow < p.N;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    const float c = p.scale_log2;
+    float m_run = -INFINITY, l = 0.f;
+    bool ok = true;
+
+    for (int i = 0; ok && i < n; i++) {
+      const int sb = i & 1;
+      if (!mbar_wait(bar_sfull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) { ok = false; break; }
+      if (i >= 2 &&
+          !mbar_wait(bar_pvdone(sb), ((i - 2) >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int tok0 = static_cast<int>(un.ids[i]) * p.kvb - p.kv_pad_head;
+      const int lo = max(0, -tok0), hi = min(p.kvb, p.N - tok0);
+      const bool act = row_valid && ((un.masks[i] >> grp) & 1) && hi > lo;
+      const uint32_t s_addr = lane_addr + FW_COL_S + sb * 128;
+      const uint32_t p_addr = lane_addr + FW_COL_P + sb * 64;
+      if (__any_sync(0xffffffffu, act)) {
+        float mt = -INFINITY;
+        for (int c0 = 0; c0 < p.kvb; c0 += 16) {
+          uint32_t v[16];
+          tmem_ld16(s_addr + c0, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int x = 0; x < 16; x++)
+            if (c0 + x >= lo && c0 + x < hi) mt = fmaxf(mt, __uint_as_float(v[x]));
+        }
+        const float mt2 = act ? mt * c : -INFINITY;
+        const bool grow = act && (mt2 > m_run + 8.f || m_run == -INFINITY);
+        const float m_new = grow ? mt2 : m_run;
+        const bool resc = grow && l > 0.f;
+        if (__any_sync(0xffffffffu, resc)) {
+          // O is only safe to touch once every PV issued so far has retired
+          if (!mbar_wait(bar_pvdone((i - 1) & 1), ((i - 1) >> 1) & 1, w,
+                         FTK_DEV_TIMEOUT_CONSUMER)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const float alpha = resc ? fast_exp2(m_run - m_new) : 1.f;
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(lane_addr + FW_COL_O + c0, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int x = 0; x < 32; x++) v[x] = __float_as_uint(__uint_as_float(v[x]) * alpha);
+            tmem_st32(lane_addr + FW_COL_O + c0, v);
+          }
+          tmem_wait_st();
+          l *= alpha;
+        }
+        m_run = m_new;
+        for (int c0 = 0; c0 < p.kvb; c0 += 16) {
+          uint32_t v[16];
+          tmem_ld16(s_addr + c0, v);
+          tmem_wait_ld();
+          uint32_t pk[8];
+#pragma unroll
+          for (int x = 0; x < 16; x += 2) {
+            float p0 = 0.f, p1 = 0.f;
+            if (act && c0 + x >= lo && c0 + x < hi)
+              p0 = fast_exp2(fmaf(__uint_as_float(v[x]), c, -m_run));
+            if (act && c0 + x + 1 >= lo && c0 + x + 1 < hi)
+              p1 = fast_exp2(fmaf(__uint_as_float(v[x + 1]), c, -m_run));
+            l += p0 + p1;
+            pk[x >> 1] = pack2(p0, p1, p.fmt);
+          }
+          tmem_st8(p_addr + (c0 >> 1), pk);
+        }
+      } else {
+        uint32_t z[8];
+#pragma unroll
+        for (int x = 0; x < 8; x++) z[x] = 0u;
+        for (int c0 = 0; c0 < p.kvb; c0 += 16) tmem_st8(p_addr + (c0 >> 1), z);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_pfull(sb));
+    }
+
+    // ------------------------------------------------------------ epilogue
+    if (ok && n > 0)
+      ok = mbar_wait(bar_pvdone((n - 1) & 1), ((n - 1) >> 1) & 1, w, FTK_DEV_TIMEOUT_EPILOGUE);
+    if (ok) {
+      tc_fence_after();
+      const bool have = (n > 0) && l > 0.f;
+      const float inv = have ? 1.f / l : 0.f;
+      uint8_t* orow = nullptr;
+      if (row_valid)
+        orow = static_cast<uint8_t*>(p.o) +
+               2 * (static_cast<int64_t>(b_idx) * p.so_b + static_cast<int64_t>(qrow) * p.so_n +
+                    static_cast<int64_t>(h_idx) * p.so_h);
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t v[32];
+        if (n > 0) {
+          tmem_ld32(lane_addr + FW_COL_O + c0, v);
+          tmem_wait_ld();
+        }
+        if (row_valid) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int x = 0; x < 32; x += 2) {
+            const float a = have ? __uint_as_float(v[x]) * inv : 0.f;
+            const float b = have ? __uint_as_float(v[x + 1]) * inv : 0.f;
+            pk[x >> 1] = pack2(a, b, p.fmt);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(orow + c0 * 2);
+#pragma unroll
+          for (int x = 0; x < 4; x++)
+            dst[x] = make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]);
+        }
+      }
+      if (row_valid)
+        p.lse[static_cast<int64_t>(bh) * p.N + qrow] =
+            have ? (m_run + log2f(l)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag)
+    for (int i = 0; i < 200; i++) __nanosleep(1000);
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+template <int D>
+static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                      FwdParams p, int64_t BH, cudaStream_t st) {
+  constexpr int NCH = D / 64;
+  const int stage_bytes = 2 * NCH * p.kvb * 128;
+  int nst = std::min(FW_MAX_STAGES, (168 * 1024) / stage_bytes);
+  if (nst < 2) return FTK_ERR_UNSUPPORTED;
+  p.nstages = nst;
+  const size_t smem = 1024 + NCH * 128 * 128 + static_cast<size_t>(nst) * stage_bytes;
+  if (cudaFuncSetAttribute(sparse_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return FTK_ERR_CUDA;
+  dim3 grid((p.QM + p.G - 1) / p.G, static_cast<unsigned>(BH));
+  sparse_fwd_kernel<D><<<grid, FW_THREADS, smem, st>>>(tq, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+}
+
+}  // namespace ftk
+
+using namespace ftk;
+
+extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int dtype, int64_t B,
+                              int64_t H, int64_t N, int64_t D, int64_t sq_b, int64_t sq_n,
+                              int64_t sq_h, int64_t sk_b, int64_t sk_n, int64_t sk_h, int64_t sv_b,
+                              int64_t sv_n, int64_t sv_h, const int32_t* merged_idx, int QM, int W,
+                              int q_block_size, int kv_block_size, int q_pad_head, int kv_pad_head,
+                              float scale, void* o, int64_t so_b, int64_t so_n, int64_t so_h,
+                              float* lse, int32_t* status, void* stream) {
+  if (!q || !k || !v || !merged_idx || !o || !lse) return FTK_ERR_BAD_ARG;
+  if (B <= 0 || H <= 0 || N <= 0 || QM <= 0 || W <= 0) return FTK_ERR_BAD_ARG;
+  if (dtype != FTK_DTYPE_F16 && dtype != FTK_DTYPE_BF16) return FTK_ERR_BAD_ARG;
+  if (q_block_size <= 0 || kv_block_size <= 0) return FTK_ERR_BAD_ARG;
+  if (q_pad_head < 0 || q_pad_head >= q_block_size || kv_pad_head < 0 ||
+      kv_pad_head >= kv_block_size)
+    return FTK_ERR_BAD_ARG;
+  if (static_cast<int64_t>(QM) * q_block_size < q_pad_head + N) return FTK_ERR_BAD_ARG;
+  if (D != 64 && D != 128) return FTK_ERR_UNSUPPORTED;
+  if (q_block_size > 128) return FTK_ERR_UNSUPPORTED;
+  if (kv_block_size % 16 != 0 || kv_block_size > 128) return FTK_ERR_UNSUPPORTED;
+  const int64_t Mkv = (kv_pad_head + N + kv_block_size - 1) / kv_block_size;
+  if (Mkv > AT_MAX_BLOCKS) return FTK_ERR_UNSUPPORTED;
+  if (B * H > 65535) return FTK_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(o) & 15u) || (so_b & 7) || (so_n & 7) || (so_h & 7))
+    return FTK_ERR_BAD_ARG;
+
+  FwdParams p{};
+  p.N = static_cast<int>(N);
+  p.H = static_cast<int>(H);
+  p.QM = QM;
+  p.W = W;
+  p.Mkv = static_cast<int>(Mkv);
+  p.g = q_block_size;
+  p.kvb = kv_block_size;
+  p.q_pad_head = q_pad_head;
+  p.kv_pad_head = kv_pad_head;
+  p.G = std::max(1, std::min(AT_MAX_GROUPS, 128 / q_block_size));
+  p.fmt = dtype;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.merged = merged_idx;
+  p.o = o;
+  p.so_b = so_b;
+  p.so_n = so_n;
+  p.so_h = so_h;
+  p.lse = lse;
+  p.status = status;
+
+  CUtensorMap tq, tk, tv;
+  int e = encode_tmap_bnhd(&tq, q, dtype, B, N, H, D, sq_b, sq_n, sq_h, 64, 128);
+  if (e) return e;
+  e = encode_tmap_bnhd(&tk, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, kv_block_size);
+  if (e) return e;
+  e = encode_tmap_bnhd(&tv, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, kv_block_size);
+  if (e) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (D == 64) return launch_fwd<64>(tq, tk, tv, p, B * H, st);
+  return launch_fwd<128>(tq, tk, tv, p, B * H, st);
+}

@@ -1,0 +1,108 @@
+"""CPU-side checks of the boundary: the shared library loads without a GPU,
+exports every symbol include/ftk_api.h declares, and the Python mirror raises
+the reference's exceptions before touching the device."""
+
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "ftk_api.h")
+
+
+@pytest.fixture(scope="module")
+def ftk():
+    import flash_topk_attn_v2 as m
+    return m
+
+
+def test_library_exports_every_declared_symbol(ftk):
+    from flash_topk_attn_v2 import _lib
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    declared = set(re.findall(r"\b(ftk_\w+)\s*\(", text))
+    assert len(declared) >= 15
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared:
+        assert hasattr(raw, name), f"{name} declared in ftk_api.h but not exported"
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+
+
+def test_version_and_error_text(ftk):
+    from flash_topk_attn_v2 import _lib
+    assert _lib.lib.ftk_version() >= 100
+    for code in (0, -1, -2, -3, -4, -5, 101, 105):
+        assert _lib.error_text(code) != "unknown code"
+    assert _lib.error_text(12345) == "unknown code"
+    with pytest.raises(ValueError):
+        _lib.check(-1, "x")
+    with pytest.raises(NotImplementedError):
+        _lib.check(-2, "x")
+    with pytest.raises(RuntimeError):
+        _lib.check(-4, "x")
+
+
+def test_workspace_queries_need_no_gpu(ftk):
+    from flash_topk_attn_v2 import _lib
+    lib = _lib.lib
+    a = lib.ftk_score_topk_workspace(2, 1024, 16)
+    b = lib.ftk_block_score_workspace(2, 1024)
+    assert a >= b + 2 * 1024 * 16 * 4 and b >= 2 * 2 * 1024 * 4
+    assert lib.ftk_build_reverse_workspace(4, 64, 64) >= 4 * 64 * 2 * 4
+    assert lib.ftk_sort_by_count_workspace(5000, 10) >= 11 * 3 * 4
+
+
+def test_api_names_and_signatures(ftk):
+    import inspect
+    assert ftk.__all__ == ["flash_topk_score", "build_qblock_topk_indices", "flash_topk_attn"]
+    s = inspect.signature(ftk.flash_topk_score)
+    assert list(s.parameters) == ["q", "k", "num_heads", "score_block_size", "topk", "padding",
+                                  "threshold"]
+    assert s.parameters["score_block_size"].default == 64 and s.parameters["topk"].default == 16
+    s = inspect.signature(ftk.build_qblock_topk_indices)
+    assert list(s.parameters) == ["topk_indices", "q_block_size", "q_padding", "topk_scores",
+                                  "qblock_topk"]
+    s = inspect.signature(ftk.flash_topk_attn)
+    assert list(s.parameters) == ["q", "k", "v", "merged_indices", "counts", "num_heads",
+                                  "q_block_size", "kv_block_size", "scale", "num_kv_heads",
+                                  "kv_padding", "q_padding", "S_MAX"]
+
+
+def test_reference_exceptions_before_any_launch(ftk):
+    x = torch.zeros(1, 128, 64)
+    with pytest.raises(ValueError, match="requires CUDA"):
+        ftk.flash_topk_score(x, x, num_heads=1)
+    with pytest.raises(ValueError, match="num_heads is required"):
+        ftk.flash_topk_score(x, x)
+    with pytest.raises(ValueError, match="3D"):
+        ftk.flash_topk_score(x[0], x[0], num_heads=1)
+    x4 = torch.zeros(1, 2, 128, 32)
+    with pytest.raises(ValueError, match="num_heads"):
+        ftk.flash_topk_score(x4, x4, num_heads=3)
+    idx = torch.zeros(1, 1, 100, 4, dtype=torch.int32)
+    with pytest.raises(ValueError, match="divisible"):
+        ftk.build_qblock_topk_indices(idx, 64)
+    with pytest.raises(ValueError, match="q_pad_head"):
+        ftk.build_qblock_topk_indices(idx, 64, q_padding=(64, 0))
+    with pytest.raises(ValueError, match="non-negative"):
+        ftk.build_qblock_topk_indices(idx, 64, q_padding=(-1, 0))
+    with pytest.raises(ValueError, match=r"\[B, H, N, K\]"):
+        ftk.build_qblock_topk_indices(idx[0], 64)
+    with pytest.raises(NotImplementedError, match="GQA"):
+        ftk.flash_topk_attn(x, x, x, idx, None, 1, 64, 64, num_kv_heads=2)
+    with pytest.raises(ValueError, match="requires CUDA"):
+        ftk.flash_topk_attn(x, x, x, idx, None, 1, 64, 64)
+
+
+def test_no_fallback_when_library_missing(tmp_path, monkeypatch):
+    """The package must refuse to import without its CUDA library."""
+    import importlib
+    import sys
+    from flash_topk_attn_v2 import _lib
+    monkeypatch.setattr(os.path, "exists", lambda p, _e=os.path.exists: False
+                        if p == _lib.LIB_PATH else _e(p))
+    with pytest.raises(ImportError, match="no fallback"):
+        _lib._load()

@@ -1,0 +1,232 @@
+"""GPU parity: the CUDA path (through the Python mirror -> C ABI) against the
+CPU oracle and the golden vectors, on the same seeded inputs.
+
+Bars: indices bit-exact except reported near-ties (two block scores closer
+than 1e-6 relative in the fp64 arbiter); select / merge / reverse / sort
+bit-exact when fed the same fp32 inputs; O, lse, dQ, dK, dV within 2e-3 abs /
+1e-2 rel of the fp64 oracle.
+"""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import ftk_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+ATOL, RTOL = 2e-3, 1e-2
+
+
+@pytest.fixture(scope="module")
+def ftk():
+    import flash_topk_attn_v2 as m
+    return m
+
+
+def _close(got, want, atol=ATOL, rtol=RTOL, what=""):
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    fin = np.isfinite(want)
+    assert (np.isfinite(got) == fin).all(), f"{what}: finiteness differs"
+    assert (got[~fin] == want[~fin]).all(), what
+    err = np.abs(got[fin] - want[fin])
+    bad = err > atol + rtol * np.abs(want[fin])
+    assert not bad.any(), f"{what}: {int(bad.sum())} bad, max err {float(err.max()):.3e}"
+
+
+def _inputs(cfg):
+    t = cases.make_inputs(cfg)
+    return t, {k: v.float().numpy() for k, v in t.items()}
+
+
+def _gold(name):
+    return dict(np.load(os.path.join(GOLD, f"{name}.npz")))
+
+
+@pytest.mark.parametrize("name", list(cases.GOLDEN_CASES))
+def test_block_score_and_topk(ftk, name):
+    cfg = cases.GOLDEN_CASES[name]
+    t, x = _inputs(cfg)
+    H, b, pad = cfg["H"], cfg["score_block_size"], tuple(cfg["padding"])
+    q, k = t["q"].cuda(), t["k"].cuda()
+    want = orc.block_score(x["q"], x["k"], H, b, pad, work=np.float64)
+
+    got = ftk.flash_block_score(q, k, H, b, pad).cpu().numpy()
+    ftk.check_errors()
+    np.testing.assert_allclose(got.sum(-1), 1.0, atol=2e-6)
+    np.testing.assert_allclose(got, want, rtol=3e-6, atol=1e-9)
+
+    # [B,H,N,D] layout goes through the same kernels in place
+    B, N = cfg["B"], cfg["N"]
+    q4 = q.view(B, N, H, -1).permute(0, 2, 1, 3).contiguous()
+    k4 = k.view(B, N, H, -1).permute(0, 2, 1, 3).contiguous()
+    got4 = ftk.flash_block_score(q4, k4, H, b, pad).cpu().numpy()
+    np.testing.assert_array_equal(got4, got)
+
+    idx, raw, avg = ftk.flash_topk_score(q, k, H, b, cfg["topk"], pad, cfg["threshold"])
+    ftk.check_errors()
+    oi, oraw, oavg, _ = orc.flash_topk_score(
+        x["q"], x["k"], H, b, cfg["topk"], pad, cfg["threshold"])
+    _, _, _, valid = orc.block_geometry(cfg["N"], b, pad)
+    rep = orc.classify_topk_mismatches(idx.cpu().numpy(), oi, want / valid, rel_band=1e-6)
+    assert rep["hard"] == 0, rep
+    same = idx.cpu().numpy() == oi
+    np.testing.assert_allclose(raw.cpu().numpy()[same], oraw[same], rtol=1e-5, atol=1e-9)
+    np.testing.assert_allclose(avg.cpu().numpy()[same], oavg[same], rtol=1e-5, atol=1e-10)
+    assert idx.dtype == torch.int32 and raw.dtype == torch.float32
+    assert tuple(idx.shape) == oi.shape
+
+
+@pytest.mark.parametrize("name", list(cases.GOLDEN_CASES))
+def test_select_merge_reverse_exact(ftk, name):
+    cfg = cases.GOLDEN_CASES[name]
+    gold = _gold(name)
+    b, pad = cfg["score_block_size"], tuple(cfg["padding"])
+    if not cfg.get("drop_block_scores"):
+        scores = torch.from_numpy(gold["block_scores"]).cuda()
+        for thr, k in ((cfg["threshold"], cfg["topk"]), (1.0, 0), (0.3, 2)):
+            gi, gr, ga = ftk.flash_topk_select(scores, thr, k, b, pad)
+            oi, orw, oa = orc.topk_select(gold["block_scores"], thr, k, b, pad)
+            np.testing.assert_array_equal(gi.cpu().numpy(), oi)
+            np.testing.assert_array_equal(gr.cpu().numpy(), orw)
+            np.testing.assert_array_equal(ga.cpu().numpy(), oa)
+
+    # merge from the oracle's own per-query lists (bit-exact incl. scores)
+    t, x = _inputs(cfg)
+    H = cfg["H"]
+    s32 = orc.block_score(x["q"], x["k"], H, b, pad, work=np.float32).astype(np.float32)
+    ti, _, ta = orc.topk_select(s32, cfg["threshold"], cfg["topk"], b, pad)
+    w = ta if cfg["score_weighted"] else None
+    om, oc, W, oms = orc.build_qblock_topk_indices(
+        ti, cfg["q_block_size"], tuple(cfg["q_padding"]), w, cfg["qblock_topk"])
+    gm, gc, gW = ftk.build_qblock_topk_indices(
+        torch.from_numpy(ti).cuda(), cfg["q_block_size"], tuple(cfg["q_padding"]),
+        None if w is None else torch.from_numpy(w).cuda(), cfg["qblock_topk"])
+    ftk.check_errors()
+    assert gW == W and gm.dtype == torch.int32 and gc.dtype == torch.int32
+    np.testing.assert_array_equal(gm.cpu().numpy(), om)
+    np.testing.assert_array_equal(gc.cpu().numpy(), oc)
+
+    M = (cfg["kv_padding"][0] + cfg["N"] + cfg["kv_padding"][1]) // cfg["kv_block_size"]
+    rev, rc, skv = ftk.flash_build_reverse_indices_cuda(gm, gc, M)
+    orev, orc_, oskv = orc.build_reverse_indices(om, oc, M)
+    np.testing.assert_array_equal(rev.cpu().numpy(), orev)
+    np.testing.assert_array_equal(rc.cpu().numpy(), orc_)
+    np.testing.assert_array_equal(skv.cpu().numpy(), oskv)
+    sc, ids = ftk.flash_sort_by_count_cuda(rc, H, M)
+    osc, oids = orc.sort_by_count(orc_)
+    np.testing.assert_array_equal(sc.cpu().numpy(), osc)
+    np.testing.assert_array_equal(ids.cpu().numpy(), oids)
+
+
+@pytest.mark.parametrize("name", list(cases.GOLDEN_CASES))
+def test_attention_fwd_bwd(ftk, name):
+    cfg = cases.GOLDEN_CASES[name]
+    gold = _gold(name)
+    t, x = _inputs(cfg)
+    H, g, kvb = cfg["H"], cfg["q_block_size"], cfg["kv_block_size"]
+    qpad, kvpad = tuple(cfg["q_padding"]), tuple(cfg["kv_padding"])
+    merged = gold["merged"].astype(np.int32)
+    q = t["q"].cuda().requires_grad_(True)
+    k = t["k"].cuda().requires_grad_(True)
+    v = t["v"].cuda().requires_grad_(True)
+    counts = torch.from_numpy((merged >= 0).sum(-1).astype(np.int32)).cuda()
+    o, lse = ftk.flash_topk_attn(
+        q, k, v, torch.from_numpy(merged).cuda(), counts, H, g, kvb,
+        kv_padding=kvpad, q_padding=qpad)
+    ftk.check_errors()
+    assert o.dtype == q.dtype and lse.dtype == torch.float32
+    wo, wl = orc.sparse_attn_fwd(x["q"], x["k"], x["v"], merged, H, g, kvb, None, qpad, kvpad)
+    _close(o.detach().float().cpu().numpy(), wo, what="O")
+    _close(lse.cpu().numpy(), wl, what="lse")
+    s = cfg.get("store_row_stride", 1)
+    _close(o.detach().float().cpu().numpy()[:, ::s], gold["o_diff"], what="O vs golden")
+
+    o.backward(t["do"].cuda())
+    ftk.check_errors()
+    o_rounded = o.detach().float().cpu().numpy()
+    wq, wk, wv = orc.sparse_attn_bwd(
+        x["q"], x["k"], x["v"], o_rounded, wl, x["do"], merged, H, g, kvb, None, qpad, kvpad)
+    _close(q.grad.float().cpu().numpy(), wq, what="dQ")
+    _close(k.grad.float().cpu().numpy(), wk, what="dK")
+    _close(v.grad.float().cpu().numpy(), wv, what="dV")
+    _close(q.grad.float().cpu().numpy()[:, ::s], gold["dq"], what="dQ vs golden")
+    _close(k.grad.float().cpu().numpy()[:, ::s], gold["dk"], what="dK vs golden")
+    _close(v.grad.float().cpu().numpy()[:, ::s], gold["dv"], what="dV vs golden")
+
+
+def test_attention_empty_and_partial_lists(ftk):
+    """q-blocks with no candidates give O = 0, lse = -inf and zero gradients;
+    neighbours with different lists share a tile without leaking."""
+    cfg = dict(B=1, N=256, H=2, D=64, dtype="bf16", seed=3, do_seed=4)
+    t = cases.make_inputs(cfg)
+    x = {k: v.float().numpy() for k, v in t.items()}
+    g, kvb, QM, M = 64, 64, 4, 4
+    merged = np.full((1, 2, QM, 4), -1, dtype=np.int32)
+    merged[0, 0, 0, :2] = [3, 0]
+    merged[0, 0, 1, :1] = [1]          # same tile as q-block 0, different list
+    merged[0, 0, 3, :4] = [2, 0, 1, 3]
+    merged[0, 1, 2, :1] = [2]          # head 1: only q-block 2 attends
+    q = t["q"].cuda().requires_grad_(True)
+    k = t["k"].cuda().requires_grad_(True)
+    v = t["v"].cuda().requires_grad_(True)
+    o, lse = ftk.flash_topk_attn(q, k, v, torch.from_numpy(merged).cuda(), None, 2, g, kvb)
+    wo, wl = orc.sparse_attn_fwd(x["q"], x["k"], x["v"], merged, 2, g, kvb)
+    _close(o.detach().float().cpu().numpy(), wo, what="O")
+    _close(lse.cpu().numpy(), wl, what="lse")
+    assert torch.isinf(lse[0, 0, 128:192]).all() and (o[0, 128:192, :64] == 0).all()
+    o.backward(t["do"].cuda())
+    ftk.check_errors()
+    wq, wk, wv = orc.sparse_attn_bwd(
+        x["q"], x["k"], x["v"], o.detach().float().cpu().numpy(), wl, x["do"], merged, 2, g, kvb)
+    _close(q.grad.float().cpu().numpy(), wq, what="dQ")
+    _close(k.grad.float().cpu().numpy(), wk, what="dK")
+    _close(v.grad.float().cpu().numpy(), wv, what="dV")
+
+
+def test_score_overflow_fallback(ftk):
+    """Logits far above the first key tile's maximum overflow the single-pass
+    sums; the exact two-pass fallback must take over."""
+    g = torch.Generator().manual_seed(7)
+    B, N, H, D = 1, 512, 1, 64
+    q = torch.randn(B, N, H * D, generator=g)
+    k = torch.randn(B, N, H * D, generator=g)
+    k[:, 300:] *= 40.0                  # later tiles dominate by hundreds of nats
+    q *= 3.0
+    qh, kh = q.half(), k.half()
+    want = orc.block_score(qh.float().numpy(), kh.float().numpy(), H, 64, (0, 0))
+    got = ftk.flash_block_score(qh.cuda(), kh.cuda(), H, 64).cpu().numpy()
+    ftk.check_errors()
+    assert np.isfinite(got).all()
+    np.testing.assert_allclose(got, want, rtol=2e-4, atol=1e-7)
+
+
+def test_error_codes_through_c_abi(ftk):
+    """The C entry points validate before launching anything."""
+    from flash_topk_attn_v2 import _lib
+    lib = _lib.lib
+    x = torch.zeros(1, 128, 64, dtype=torch.float16, device="cuda")
+    ws = torch.empty(lib.ftk_block_score_workspace(1, 128), dtype=torch.uint8, device="cuda")
+    out = torch.empty(1, 1, 128, 2, device="cuda")
+    args = lambda bsz, D, wsz: (x.data_ptr(), x.data_ptr(), 0, 1, 1, 128, D, 128 * 64, 64, 64,
+                                128 * 64, 64, 64, 0, 1, bsz, 0, 0, 0.125, out.data_ptr(),
+                                ws.data_ptr(), wsz, 0, 0)
+    assert lib.ftk_block_score(*args(64, 64, ws.numel())) == 0
+    assert lib.ftk_block_score(*args(48, 64, ws.numel())) == -1      # 128 % 48 != 0
+    assert lib.ftk_block_score(*args(8, 64, ws.numel())) == -2       # block size not /16
+    assert lib.ftk_block_score(*args(64, 96, ws.numel())) == -2      # head dim
+    assert lib.ftk_block_score(*args(64, 64, 16)) == -3              # workspace
+    torch.cuda.synchronize()
+    with pytest.raises(ValueError):
+        ftk.flash_topk_score(x, x)                                   # num_heads missing
+    with pytest.raises(ValueError):
+        ftk.flash_topk_score(x, x, 1, 64, 16, (64, 0))
+    with pytest.raises(NotImplementedError):
+        ftk.flash_topk_attn(x, x, x, None, None, 1, 64, 64, num_kv_heads=2)
+    with pytest.raises(ValueError):
+        ftk.build_qblock_topk_indices(torch.zeros(1, 1, 100, 4, dtype=torch.int32).cuda(), 64)
