@@ -1,0 +1,386 @@
+#!/usr/bin/env python
+"""Benchmark of the flash_topk_attn_v2 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one pass of the path over one batch of synthetic input:
+flash_topk_score -> build_qblock_topk_indices -> flash_topk_attn -> backward,
+at B=1 (per GPU), N=32768, H=32, D=128, bf16, score block 64, topk 32,
+threshold 0.9, q/kv block 64 (the shape the headline metric is quoted on).
+Rank r draws its own batch element (seed r); ranks never exchange data, so
+scaling is weak: `value` is the tokens all ranks processed per second of the
+slowest rank's device time.
+
+`--impl reference` times the CPU restatement of the reference's dense PyTorch
+path (oracle/) on the host cores over a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "flash-topk-attention_b200"))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+WORKLOAD = dict(
+    name="config2-e2e", B=1, N=32768, H=32, D=128, dtype="bf16", input_scale=0.5,
+    score_block_size=64, topk=32, threshold=0.9, q_block_size=64, kv_block_size=64,
+)
+METRIC = "score+sparse fwd+bwd tokens/s @N=32k,H=32,D=128 bf16"
+UNIT = "tokens/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(hbm=d["hbm_gbs"], tf=d["bf16_tflops"], tf_sus=d["bf16_tflops_sustained"],
+                    src="measured")
+    return dict(hbm=6650.0, tf=1590.0, tf_sus=1400.0, src="fallback")
+
+
+# ---------------------------------------------------------------------------
+# synthetic inputs
+# ---------------------------------------------------------------------------
+def make_host_inputs(cfg, seed):
+    g = torch.Generator().manual_seed(seed)
+    shape = (cfg["B"], cfg["N"], cfg["H"] * cfg["D"])
+    s = cfg["input_scale"]
+    out = {}
+    for name in ("q", "k", "v"):
+        out[name] = (torch.randn(shape, generator=g) * s).to(torch.bfloat16).pin_memory()
+    g2 = torch.Generator().manual_seed(1000 + seed)
+    out["do"] = torch.randn(shape, generator=g2).to(torch.bfloat16).pin_memory()
+    return out
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+def run_ours(args):
+    import flash_topk_attn_v2 as ftk
+    from flash_topk_attn_v2 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    cfg = dict(WORKLOAD)
+    if args.small:
+        cfg.update(N=4096, H=8, name="small")
+    H, D, N, B = cfg["H"], cfg["D"], cfg["N"], cfg["B"]
+    b, K, thr = cfg["score_block_size"], cfg["topk"], cfg["threshold"]
+    g, kvb = cfg["q_block_size"], cfg["kv_block_size"]
+    host = make_host_inputs(cfg, seed=rank)
+    devt = {k: torch.empty_like(v, device=dev) for k, v in host.items()}
+    for k in devt:
+        devt[k].copy_(host[k])
+    host_out = {k: torch.empty_like(host["q"]).pin_memory() for k in ("o", "dq", "dk", "dv")}
+
+    stage_ms = {"score_select": 0.0, "merge": 0.0, "sparse_fwd": 0.0, "sparse_bwd": 0.0}
+    pairs = [0]
+
+    def step(record):
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(5)] if record else None
+        q = devt["q"].detach().requires_grad_(True)
+        k = devt["k"].detach().requires_grad_(True)
+        v = devt["v"].detach().requires_grad_(True)
+        if record:
+            evs[0].record()
+        idx, raw, avg = ftk.flash_topk_score(q.detach(), k.detach(), H, b, K, (0, 0), thr)
+        if record:
+            evs[1].record()
+        merged, counts, W = ftk.build_qblock_topk_indices(idx, g, topk_scores=avg)
+        if record:
+            evs[2].record()
+        o, lse = ftk.flash_topk_attn(q, k, v, merged, counts, H, g, kvb)
+        if record:
+            evs[3].record()
+        o.backward(devt["do"])
+        if record:
+            evs[4].record()
+        return evs, (o, q.grad, k.grad, v.grad, counts)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        _, res = step(False)
+    torch.cuda.synchronize()
+    ftk.check_errors()
+    pairs[0] = int(res[4].sum().item())
+
+    # ---- device-resident timing -------------------------------------------
+    sampler = ClockSampler(local)
+    launches0 = ops.launch_count()
+    barrier()
+    sampler.start()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    all_evs = []
+    t0.record()
+    for _ in range(args.steps):
+        evs, res = step(True)
+        all_evs.append(evs)
+    t1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    launches = ops.launch_count() - launches0
+    ms = t0.elapsed_time(t1)
+    for evs in all_evs:
+        for i, nm in enumerate(stage_ms):
+            stage_ms[nm] += evs[i].elapsed_time(evs[i + 1]) / args.steps
+    ftk.check_errors()
+
+    # ---- end to end: host buffers in, host buffers out --------------------
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        for k in devt:
+            devt[k].copy_(host[k], non_blocking=True)
+        _, res = step(False)
+        for nm, t in zip(("o", "dq", "dk", "dv"), res[:4]):
+            host_out[nm].copy_(t, non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1)
+    ftk.check_errors()
+
+    if dist is not None:
+        tt = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(tt[0]), float(tt[1])
+    tokens_per_step = world * B * N
+    value = tokens_per_step * args.steps / (ms / 1e3)
+    e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
+    bytes_in = sum(v.numel() * v.element_size() for v in host.values())
+    bytes_out = sum(v.numel() * v.element_size() for v in host_out.values())
+
+    if rank == 0:
+        peaks = measured_peaks()
+        P = pairs[0]
+        unit_flops = D * g * kvb * P           # one GEMM over every (q-block, kv-block) pair
+        kern = {
+            "score": dict(ms=stage_ms["score_select"], flops=2.0 * B * H * N * N * D),
+            "sparse_fwd": dict(ms=stage_ms["sparse_fwd"], flops=4.0 * unit_flops),
+            "sparse_bwd": dict(ms=stage_ms["sparse_bwd"], flops=10.0 * unit_flops),
+        }
+        for d in kern.values():
+            d["tflops"] = d["flops"] / (d["ms"] * 1e-3) / 1e12 if d["ms"] > 0 else 0.0
+            d["frac_of_measured_sustained"] = d["tflops"] / peaks["tf_sus"]
+        dom = max(kern, key=lambda n: kern[n]["ms"])
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": cfg["name"], "B_per_gpu": B, "N": N, "H": H, "D": D,
+                       "score_block_size": b, "topk": K, "threshold": thr, "q_block_size": g,
+                       "kv_block_size": kvb, "sharding": "batch x head slices, no collective",
+                       "l2": "inputs larger than L2 (4 x 268 MB per step)",
+                       "candidate_pairs_per_step": P},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": bytes_in,
+                    "d2h_bytes_per_step": bytes_out, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches,
+            "stage_ms": stage_ms,
+            "roofline": {"bound": "tensor", "kernel": dom, "achieved": kern[dom]["tflops"],
+                         "peak": peaks["tf_sus"], "unit": "TFLOP/s",
+                         "frac": kern[dom]["tflops"] / peaks["tf_sus"], "traffic": None,
+                         "peak_source": peaks["src"] + " sustained bf16",
+                         "all": {n: {"ms": d["ms"], "tflops": d["tflops"],
+                                     "frac": d["frac_of_measured_sustained"]}
+                                 for n, d in kern.items()}},
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(cfg, seconds=args.cpu_seconds)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------
+# CPU arm (the oracle port, reported baseline only)
+# ---------------------------------------------------------------------------
+def cpu_sample_step(cfg, x, rows):
+    """One bounded sample: `rows` query rows of one (batch, head) slice through
+    score -> select -> merge -> sparse fwd -> bwd, fp32 numpy on all cores."""
+    from oracle import ftk_oracle as orc
+    b, K, thr = cfg["score_block_size"], cfg["topk"], cfg["threshold"]
+    g, kvb, N = cfg["q_block_size"], cfg["kv_block_size"], cfg["N"]
+    q, k, v, do = x
+    M = N // b
+    scale = np.float32(cfg["D"] ** -0.5)
+    s = (q[:rows] * scale) @ k.T
+    s -= s.max(axis=1, keepdims=True)
+    np.exp(s, out=s)
+    s /= s.sum(axis=1, keepdims=True)
+    scores = s.reshape(rows, M, b).sum(-1)[None, None]
+    idx, raw, avg = orc.topk_select(scores, thr, K, b)
+    merged, counts, W, _ = orc.build_qblock_topk_indices(idx, g, (0, 0), avg, None)
+    # attention over the sampled q-blocks only; keys/values are the full slice
+    qm = rows // g
+    pad_rows = np.zeros((N - rows, q.shape[1]), dtype=np.float32)
+    qfull = np.concatenate([q[:rows], pad_rows])[None]
+    dofull = np.concatenate([do[:rows], pad_rows])[None]
+    mfull = np.full((1, 1, N // g, W), -1, dtype=np.int32)
+    mfull[0, 0, :qm] = merged[0, 0]
+    o, lse = orc.sparse_attn_fwd(qfull, k[None], v[None], mfull, 1, g, kvb, work=np.float32)
+    orc.sparse_attn_bwd(qfull, k[None], v[None], o, lse, dofull, mfull, 1, g, kvb,
+                        work=np.float32)
+    return rows
+
+
+def cpu_baseline(cfg, seconds=15.0, rows=512):
+    N, H, D = cfg["N"], cfg["H"], cfg["D"]
+    g = torch.Generator().manual_seed(0)
+    x = [(torch.randn(N, D, generator=g) * cfg["input_scale"]).to(torch.bfloat16).float().numpy()
+         for _ in range(4)]
+    rows = min(rows, N)
+    cpu_sample_step(cfg, x, min(rows, 128))  # warm
+    t0 = time.perf_counter()
+    done = 0
+    while True:
+        done += cpu_sample_step(cfg, x, rows)
+        el = time.perf_counter() - t0
+        if el > seconds or done >= N:
+            break
+    # `done` rows of ONE head took `el` seconds; a token needs all H heads
+    return {"value": done / H / el, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{done} query rows of one (batch, head) slice, full key length {N}, "
+                      f"score+select+merge+sparse fwd+bwd in fp32 numpy ({el:.1f} s); "
+                      f"extrapolated to {H} heads"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = dict(WORKLOAD)
+    N, H, D = cfg["N"], cfg["H"], cfg["D"]
+    g = torch.Generator().manual_seed(0)
+    x = [(torch.randn(N, D, generator=g) * cfg["input_scale"]).to(torch.bfloat16).float().numpy()
+         for _ in range(4)]
+    rows = 256
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_sample_step(cfg, x, 128)
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(args.steps):
+        done += cpu_sample_step(cfg, x, rows)
+    el = time.perf_counter() - t0
+    value = done / H / el
+    sample = (f"each step = {rows} query rows of one (batch, head) slice against all {N} keys, "
+              f"extrapolated to {H} heads")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": cfg["name"], "B_per_gpu": cfg["B"], "N": N, "H": H, "D": D,
+                   "score_block_size": cfg["score_block_size"], "topk": cfg["topk"],
+                   "threshold": cfg["threshold"], "q_block_size": cfg["q_block_size"],
+                   "kv_block_size": cfg["kv_block_size"]},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--small", action="store_true", help="N=4096, H=8 (profiling-sized case)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

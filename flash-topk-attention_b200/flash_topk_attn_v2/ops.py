@@ -21,6 +21,17 @@ from ._lib import check, lib, ptr, stream_ptr
 _SCORE_SCRATCH_BYTES = int(os.environ.get("FTK_SCORE_SCRATCH_BYTES", 4 << 30))
 _DEBUG = os.environ.get("FTK_DEBUG", "0") not in ("", "0")
 _status_words = {}
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of libftk_sm100.so enqueued by this process so far."""
+    return _launches
+
+
+def _count(n: int) -> None:
+    global _launches
+    _launches += n
 
 
 def status_word(device) -> torch.Tensor:
@@ -181,6 +192,7 @@ def flash_block_score(q, k, num_heads, score_block_size, padding=(0, 0)):
             ptr(qq), ptr(kk), _lib.dtype_code(qq), B, H, N, Dk, *sq, *sk, b0, cnt,
             score_block_size, ph, pt, float(D) ** -0.5, ptr(flat[b0]), ptr(ws), ws.numel(),
             ptr(status), stream_ptr(q.device)), "ftk_block_score")
+        _count(4)
     _after(q.device)
     return out
 
@@ -227,6 +239,7 @@ def flash_topk_select(block_scores, threshold, max_topk, score_block_size, paddi
         ptr(scores), 0, B * H * N, M, max_topk, score_block_size, pad_head, pad_tail,
         float(threshold), ptr(idx), ptr(raw), ptr(avg), ptr(status_word(dev)), stream_ptr(dev)),
         "ftk_topk_select")
+    _count(1)
     _after(dev)
     return idx, raw, avg
 
@@ -257,6 +270,7 @@ def flash_topk_score_fused(q, k, num_heads, score_block_size, topk, padding, thr
             score_block_size, ph, pt, float(D) ** -0.5, topk, float(threshold),
             ptr(fi[b0]), ptr(fr[b0]), ptr(fa[b0]), ptr(ws), ws.numel(), ptr(status),
             stream_ptr(dev)), "ftk_score_topk")
+        _count(4)
     _after(dev)
     # lets build_qblock_topk_indices size its table without a device round trip
     idx._ftk_num_score_blocks = M
@@ -301,6 +315,7 @@ def flash_qblock_merge(topk_indices, topk_scores, q_block_size, qblock_topk, num
         ptr(idx), ptr(scr), B * H, N, K, q_block_size, qh, qt, num_score_blocks, qblock_topk,
         ptr(merged), ptr(mscores), ptr(counts), ptr(status_word(dev)), stream_ptr(dev)),
         "ftk_qblock_merge")
+    _count(1)
     _after(dev)
     if return_counts:
         return merged, mscores, counts
@@ -327,6 +342,7 @@ def flash_build_reverse_indices_cuda(merged_indices, counts, num_kv_blocks):
     check(lib.ftk_build_reverse(
         ptr(merged), ptr(cnt), B * H, QM, W, M, ptr(rev), ptr(rc), ptr(skv), ptr(ws), ws.numel(),
         ptr(status_word(dev)), stream_ptr(dev)), "ftk_build_reverse")
+    _count(3)
     _after(dev)
     return rev, rc, skv
 
@@ -345,6 +361,7 @@ def flash_sort_by_count_cuda(reverse_counts, num_heads, num_kv_blocks):
     ws = torch.empty(lib.ftk_sort_by_count_workspace(total, max_val), dtype=torch.uint8, device=dev)
     check(lib.ftk_sort_by_count(ptr(flat), total, max_val, ptr(sc), ptr(ids), ptr(ws), ws.numel(),
                                 stream_ptr(dev)), "ftk_sort_by_count")
+    _count(3)
     return sc, ids
 
 
@@ -384,6 +401,7 @@ class FlashSparseAttnFunc(torch.autograd.Function):
             ptr(merged), QM, W, q_block_size, kv_block_size, q_pad_head, kv_pad_head,
             float(scale), ptr(o), N * C, C, D, ptr(lse), ptr(status_word(dev)),
             stream_ptr(dev)), "ftk_sparse_fwd")
+        _count(1)
         _after(dev)
         ctx.save_for_backward(qq, kk, vv, o, lse, merged)
         ctx.meta = (H, D, q_block_size, kv_block_size, float(scale), q_pad_head, kv_pad_head,
@@ -414,6 +432,7 @@ class FlashSparseAttnFunc(torch.autograd.Function):
             sq_b, sq_n, sq_h, sk_b, sk_n, sk_h, sv_b, sv_n, sv_h, N * C, C, D,
             sdo_b, sdo_n, sdo_h, ptr(merged), QM, W, g, kvb, qph, kph, scale,
             ptr(lse), ptr(delta), ptr(dq), N * C, C, D, ptr(status), st), "ftk_sparse_bwd_dq")
+        _count(2)
         rev, rc, skv = flash_build_reverse_indices_cuda(merged, None, M)
         check(lib.ftk_sparse_bwd_dkv(
             ptr(qq), ptr(kk), ptr(vv), ptr(do), dt, B, H, N, D,
@@ -421,6 +440,7 @@ class FlashSparseAttnFunc(torch.autograd.Function):
             ptr(rev), ptr(rc), ptr(skv), QM, M, g, kvb, qph, kph, scale,
             ptr(lse), ptr(delta), ptr(dk), N * C, C, D, ptr(dv), N * C, C, D, ptr(status), st),
             "ftk_sparse_bwd_dkv")
+        _count(1)
         _after(dev)
         return dq, dk, dv, None, None, None, None, None, None, None, None
 
