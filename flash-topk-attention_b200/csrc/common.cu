@@ -12,6 +12,8 @@ extern "C" const char* ftk_error_string(int code) {
     case ftk::FTK_ERR_WORKSPACE: return "workspace missing or too small";
     case ftk::FTK_ERR_CUDA: return "CUDA runtime call or kernel launch failed";
     case ftk::FTK_ERR_DRIVER: return "tensor-map encoding unavailable or failed";
+    case ftk::FTK_ERR_CAPACITY:
+      return "problem exceeds the fixed buffer of a no-allocation entry point";
     case ftk::FTK_DEV_TIMEOUT_TMA: return "device: TMA producer wait timed out";
     case ftk::FTK_DEV_TIMEOUT_MMA: return "device: UMMA issuer wait timed out";
     case ftk::FTK_DEV_TIMEOUT_CONSUMER: return "device: consumer wait timed out";

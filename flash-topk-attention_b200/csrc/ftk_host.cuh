@@ -19,6 +19,7 @@ enum : int {
   FTK_ERR_WORKSPACE = -3,
   FTK_ERR_CUDA = -4,
   FTK_ERR_DRIVER = -5,
+  FTK_ERR_CAPACITY = -6,
 };
 
 enum : int { FTK_DTYPE_F16 = 0, FTK_DTYPE_BF16 = 1 };

@@ -548,3 +548,76 @@ extern "C" int ftk_sort_by_count(const int32_t* counts, int64_t total, int max_c
                                           sorted_ids);
   return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
 }
+
+// ------------------------------------------------- reverse index, no allocation
+// Some callers of this library cannot hand it a workspace because they cannot
+// allocate device memory at the point of the call: code running inside a
+// memory-pool callback, a plugin whose host gives it fixed input/output
+// buffers only, or a latency-critical loop that must never enter the
+// allocator.  For them this entry point does what ftk_build_reverse does, with
+// the membership bitmap kept in a fixed array that is part of the loaded
+// library image (FTK_NOALLOC_REVERSE_BYTES on every GPU that loads the
+// library, held until the process exits).
+//
+// In host code the array's name is only a handle, not a device address, so
+// the address is looked up per device with cudaGetSymbolAddress the first time
+// the entry point runs on that device (with that device current) and cached.
+// That first call should come before any stream capture.  The array is shared
+// by every call and keeps the previous call's bits: the part a call needs is
+// cleared on the caller's stream first.  Two calls whose GPU work overlaps
+// (different streams, or different host threads) race on it.
+constexpr size_t FTK_NOALLOC_REVERSE_BYTES = 4u << 20;  // 4 MiB
+constexpr int FTK_NOALLOC_MAX_DEVICES = 64;
+static __device__ __align__(256) unsigned g_noalloc_reverse_bits[FTK_NOALLOC_REVERSE_BYTES / 4];
+
+static std::mutex g_noalloc_mutex;
+static unsigned* g_noalloc_ptr[FTK_NOALLOC_MAX_DEVICES] = {nullptr};
+
+extern "C" size_t ftk_build_reverse_noalloc_capacity(void) { return FTK_NOALLOC_REVERSE_BYTES; }
+
+extern "C" int ftk_build_reverse_noalloc(const int32_t* merged_idx, const int32_t* counts,
+                                         int64_t BH, int QM, int W, int M, int32_t* reverse_idx,
+                                         int32_t* reverse_counts, int32_t* sorted_kv,
+                                         int32_t* status, void* stream) {
+  if (!merged_idx || !reverse_idx || !reverse_counts) return FTK_ERR_BAD_ARG;
+  if (BH <= 0 || QM <= 0 || W <= 0 || M <= 0) return FTK_ERR_BAD_ARG;
+  if (sorted_kv && M > 8192) return FTK_ERR_UNSUPPORTED;
+  const int words = (QM + 31) / 32;
+  const size_t need = static_cast<size_t>(BH) * M * words * 4;
+  // larger problems must use ftk_build_reverse with a caller-owned workspace
+  if (need > FTK_NOALLOC_REVERSE_BYTES) return FTK_ERR_CAPACITY;
+
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return FTK_ERR_CUDA;
+  if (dev < 0 || dev >= FTK_NOALLOC_MAX_DEVICES) return FTK_ERR_UNSUPPORTED;
+  unsigned* bits = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[dev]) {
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_noalloc_reverse_bits) != cudaSuccess || !p)
+        return FTK_ERR_CUDA;
+      g_noalloc_ptr[dev] = static_cast<unsigned*>(p);
+    }
+    bits = g_noalloc_ptr[dev];
+  }
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(bits, 0, need, st) != cudaSuccess) return FTK_ERR_CUDA;
+  const int64_t total_qb = BH * QM, total_kv = BH * M;
+  reverse_mark_kernel<<<static_cast<unsigned>((total_qb * 32 + 255) / 256), 256, 0, st>>>(
+      merged_idx, counts, total_qb, QM, W, M, words, bits, status);
+  reverse_list_kernel<<<static_cast<unsigned>((total_kv * 32 + 255) / 256), 256, 0, st>>>(
+      bits, total_kv, QM, words, reverse_idx, reverse_counts);
+  if (sorted_kv) {
+    const int Mp = std::max(32, next_pow2(M));
+    const size_t smem = static_cast<size_t>(Mp) * 8;
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(reverse_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return FTK_ERR_CUDA;
+    reverse_sort_kernel<<<static_cast<unsigned>(BH), 256, smem, st>>>(reverse_counts, M, Mp,
+                                                                     sorted_kv);
+  }
+  return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+}

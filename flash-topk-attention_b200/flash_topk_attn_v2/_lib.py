@@ -35,6 +35,8 @@ SIGNATURES = {
     "ftk_max_index_plus1": (i32, [vp, i64, vp, vp]),
     "ftk_build_reverse_workspace": (sz, [i64, i32, i32]),
     "ftk_build_reverse": (i32, [vp, vp, i64, i32, i32, i32, vp, vp, vp, vp, sz, vp, vp]),
+    "ftk_build_reverse_noalloc_capacity": (sz, []),
+    "ftk_build_reverse_noalloc": (i32, [vp, vp, i64, i32, i32, i32, vp, vp, vp, vp, vp]),
     "ftk_sort_by_count_workspace": (sz, [i64, i32]),
     "ftk_sort_by_count": (i32, [vp, i64, i32, vp, vp, vp, sz, vp]),
     "ftk_sparse_fwd": (i32, [vp, vp, vp, i32, i64, i64, i64, i64, *_STRIDES3, *_STRIDES3,

@@ -41,6 +41,7 @@ extern "C" {
 #define FTK_ERR_WORKSPACE (-3)    /* workspace pointer NULL or too small      */
 #define FTK_ERR_CUDA (-4)         /* a CUDA runtime call or launch failed     */
 #define FTK_ERR_DRIVER (-5)       /* tensor-map encoding unavailable / failed */
+#define FTK_ERR_CAPACITY (-6)     /* problem larger than a fixed built-in buffer */
 
 #define FTK_DEV_TIMEOUT_TMA 101
 #define FTK_DEV_TIMEOUT_MMA 102
@@ -140,6 +141,27 @@ int ftk_build_reverse(const int32_t* merged_idx, const int32_t* counts, int64_t 
                       int W, int M, int32_t* reverse_idx, int32_t* reverse_counts,
                       int32_t* sorted_kv, void* workspace, size_t workspace_bytes,
                       int32_t* status, void* stream);
+
+/* No counterpart in the reference.  ftk_build_reverse for callers that cannot
+ * allocate device memory where they call it (inside an allocator callback, in
+ * a plugin that is only handed input and output buffers, in a loop that must
+ * never enter the allocator): same inputs, outputs and results, but the
+ * membership bitmap lives in a fixed 4 MiB array inside the library image
+ * (present on every GPU that loads the library until the process exits), so
+ * there is no workspace argument and nothing is allocated or freed.
+ * Limit: BH * M * ceil(QM / 32) * 4 bytes <= ftk_build_reverse_noalloc_capacity();
+ * beyond it the call returns FTK_ERR_CAPACITY and launches nothing -- use
+ * ftk_build_reverse.  The first call on each device looks up the array's
+ * device address (cudaGetSymbolAddress, with that device current); make that
+ * call before any stream capture begins.  All calls share the one array, which
+ * is cleared on `stream` at the start of each call: calls whose GPU work can
+ * overlap (other streams, other threads) race and must be serialised by the
+ * caller. */
+size_t ftk_build_reverse_noalloc_capacity(void);
+int ftk_build_reverse_noalloc(const int32_t* merged_idx, const int32_t* counts, int64_t BH,
+                              int QM, int W, int M, int32_t* reverse_idx,
+                              int32_t* reverse_counts, int32_t* sorted_kv, int32_t* status,
+                              void* stream);
 
 /* Replaces sort_by_count_launch (csrc/sort_by_count.cpp:3-9,
  * csrc/sort_by_count_kernel.cu:12): global stable descending sort of `total`
