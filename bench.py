@@ -139,7 +139,7 @@ def run_ours(args):
 
     cfg = dict(WORKLOAD)
     if args.small:
-        cfg.update(N=4096, H=8, name="small")
+        cfg.update(N=8192, H=16, name="small")
     H, D, N, B = cfg["H"], cfg["D"], cfg["N"], cfg["B"]
     b, K, thr = cfg["score_block_size"], cfg["topk"], cfg["threshold"]
     g, kvb = cfg["q_block_size"], cfg["kv_block_size"]
@@ -372,7 +372,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--small", action="store_true", help="N=4096, H=8 (profiling-sized case)")
+    ap.add_argument("--small", action="store_true", help="N=8192, H=16 (profiling-sized case)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     args = ap.parse_args()

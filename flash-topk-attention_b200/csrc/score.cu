@@ -30,7 +30,7 @@ namespace ftk {
 constexpr int SC_QROWS = 256;      // query rows per CTA
 constexpr int SC_KT = 128;         // key rows per tile (UMMA N)
 constexpr int SC_STAGES = 4;       // K tile ring depth
-constexpr int SC_THREADS = 320;    // 2 + 8 warps
+constexpr int SC_THREADS = 576;    // 2 + 2 x 8 warps
 constexpr int SC_CHUNK_BYTES = 128 * 128;  // 128 rows x 64 16-bit elements
 
 struct ScoreParams {
@@ -43,7 +43,7 @@ struct ScoreParams {
   int fmt;                    // 0 fp16, 1 bf16
   int mode;                   // 0 first-tile reference, 1 row max only, 2 given reference
   int H, bh_begin;
-  float scale_log2;           // log2(e) / sqrt(D)
+  float scale_log2;           // log2(e) * softmax scale
   float* sums;                // [bh_count][N][M]   unnormalised block sums
   float* row_total;           // [bh_count][N]      L
   float* row_max;             // [bh_count][N]      raw-logit row maximum (modes 1, 2)
@@ -76,6 +76,13 @@ __device__ __forceinline__ TileInfo tile_info(const ScoreParams& p, int t) {
   return ti;
 }
 
+// Which softmax group drains tile t.  Tiles alternate between the two groups;
+// when a score block spans several tiles all of them go to one group so that
+// every block sum is produced by a single thread.
+__device__ __forceinline__ int tile_owner(const ScoreParams& p, int t) {
+  return (p.tiles_per_block > 1 ? t / p.tiles_per_block : t) & 1;
+}
+
 template <int D>
 __global__ void __launch_bounds__(SC_THREADS, 1)
 score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -91,9 +98,11 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = smem + Q_BYTES;
-  __shared__ __align__(8) uint64_t bars[1 + 2 * SC_STAGES + 4];
+  __shared__ __align__(8) uint64_t bars[1 + 2 * SC_STAGES + 4 + 2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
+  __shared__ float s_mref[SC_QROWS];   // group 0 -> group 1: reference exponent
+  __shared__ float s_part[SC_QROWS];   // group 1 -> group 0: partial total / maximum
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int q0 = blockIdx.x * SC_QROWS;
@@ -106,6 +115,8 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
   auto bar_kempty = [&](int s) { return smem_u32(&bars[1 + SC_STAGES + s]); };
   auto bar_afull = [&](int s) { return smem_u32(&bars[1 + 2 * SC_STAGES + s]); };
   auto bar_aempty = [&](int s) { return smem_u32(&bars[1 + 2 * SC_STAGES + 2 + s]); };
+  const uint32_t bar_mref = smem_u32(&bars[1 + 2 * SC_STAGES + 4]);
+  const uint32_t bar_part = smem_u32(&bars[1 + 2 * SC_STAGES + 5]);
 
   if (tid == 0) {
     abort_flag = 0;
@@ -116,8 +127,10 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     }
     for (int s = 0; s < 2; s++) {
       mbar_init(bar_afull(s), 1);
-      mbar_init(bar_aempty(s), 8);  // one arrival per softmax warp
+      mbar_init(bar_aempty(s), 8);  // one arrival per warp of the draining group
     }
+    mbar_init(bar_mref, 8);
+    mbar_init(bar_part, 8);
     mbar_init_fence();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
@@ -184,8 +197,12 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     }
   } else {
     // ---------------------------------------------------- softmax threads
-    const int cw = warp - 2;               // 0..7
-    const int half = cw >> 2;              // which 128-row accumulator
+    // Two groups of 8 warps.  Each tile is drained by exactly one group (see
+    // tile_owner) so both groups run concurrently on consecutive tiles and
+    // hide each other's TMEM-load and barrier latency.
+    const int cw = warp - 2;               // 0..15
+    const int group = cw >> 3;
+    const int half = (cw >> 2) & 1;        // which 128-row accumulator
     const int quarter = warp & 3;          // TMEM lane quarter this warp may read
     const int row_in_cta = half * 128 + quarter * 32 + lane;
     const int row = q0 + row_in_cta;
@@ -203,31 +220,40 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     if (p.mode == 2) mref = ceilf(p.row_max[row_off] * c);
 
     if (p.mode == 0) {
-      // reference exponent from the row maximum over the first key tile
-      ok = mbar_wait(bar_afull(0), 0, w, FTK_DEV_TIMEOUT_CONSUMER);
-      if (ok) {
-        tc_fence_after();
-        const TileInfo ti = tile_info(p, 0);
-        const int lo = max(0, -ti.row0), hi = min(ti.used, p.N - ti.row0);
-        float mx = -INFINITY;
-        for (int c0 = 0; c0 < ti.used; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(lane_addr + static_cast<uint32_t>(half * SC_KT + c0), r);
-          tmem_wait_ld();
+      if (group == 0) {
+        // reference exponent from the row maximum over the first key tile
+        ok = mbar_wait(bar_afull(0), 0, w, FTK_DEV_TIMEOUT_CONSUMER);
+        if (ok) {
+          tc_fence_after();
+          const TileInfo ti = tile_info(p, 0);
+          const int lo = max(0, -ti.row0), hi = min(ti.used, p.N - ti.row0);
+          float mx = -INFINITY;
+          for (int c0 = 0; c0 < ti.used; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(lane_addr + static_cast<uint32_t>(half * SC_KT + c0), r);
+            tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; i++) {
-            const int col = c0 + i;
-            if (col >= lo && col < hi) mx = fmaxf(mx, __uint_as_float(r[i]));
+            for (int i = 0; i < 32; i++) {
+              const int col = c0 + i;
+              if (col >= lo && col < hi) mx = fmaxf(mx, __uint_as_float(r[i]));
+            }
           }
+          mref = ceilf(mx * c);
+          if (!(fabsf(mref) < 1e30f)) mref = 0.f;
         }
-        mref = ceilf(mx * c);
-        if (!(fabsf(mref) < 1e30f)) mref = 0.f;
+        s_mref[row_in_cta] = mref;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_mref);
+      } else {
+        ok = mbar_wait(bar_mref, 0, w, FTK_DEV_TIMEOUT_CONSUMER);
+        mref = s_mref[row_in_cta];
       }
     }
 
     float acc = 0.f;
     int j = 0, col_in_block = 0;
     for (int t = 0; ok && t < T; t++) {
+      if (tile_owner(p, t) != group) continue;
       const int a = t & 1;
       const uint32_t pa = (t >> 1) & 1;
       if (!mbar_wait(bar_afull(a), pa, w, FTK_DEV_TIMEOUT_CONSUMER)) { ok = false; break; }
@@ -290,12 +316,24 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
         }
       }
     }
-    if (ok && row_ok) {
-      if (p.mode == 1) {
-        p.row_max[row_off] = run_max;
-      } else {
-        p.row_total[row_off] = total;
-        if (!(total > 0.f && total < 3.0e38f)) atomicExch(p.fallback, 1);
+    // combine the two groups' partial results per row: group 1 publishes,
+    // group 0 adds (total) or takes the larger (maximum) and writes
+    const float mine = (p.mode == 1) ? run_max : total;
+    if (group == 1) {
+      s_part[row_in_cta] = mine;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_part);
+    } else {
+      if (ok) ok = mbar_wait(bar_part, 0, w, FTK_DEV_TIMEOUT_CONSUMER);
+      if (ok && row_ok) {
+        const float other = s_part[row_in_cta];
+        if (p.mode == 1) {
+          p.row_max[row_off] = fmaxf(mine, other);
+        } else {
+          const float tot = mine + other;
+          p.row_total[row_off] = tot;
+          if (!(tot > 0.f && tot < 3.0e38f)) atomicExch(p.fallback, 1);
+        }
       }
     }
   }
@@ -318,7 +356,7 @@ __global__ void score_normalize_kernel(const float* __restrict__ sums,
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t r = i / M;
-    out[i] = __fdiv_rn(sums[i], total[r]);
+    out[i] = sums[i] * __frcp_rn(total[r]);  // same arithmetic as the fused select path
   }
 }
 

@@ -46,7 +46,11 @@ topk_select_kernel(const float* __restrict__ scores, const float* __restrict__ r
   float* savg = sel_smem + static_cast<size_t>(warp) * 2 * Mp;
   float* sraw = savg + Mp;
   const float* in = scores + row * M;
-  const float denom = row_scale ? row_scale[row] : 1.f;
+  // unnormalised sums of the fused path are scaled by one reciprocal per row
+  const float inv_total = row_scale ? __frcp_rn(row_scale[row]) : 1.f;
+  // dividing by a power of two is exact as a multiplication: same bits, no divide
+  const bool pow2 = (bsz & (bsz - 1)) == 0;
+  const float inv_bsz = 1.f / static_cast<float>(bsz);
 
   int best_bits = __float_as_int(-1.f);
   int best_j = 0x7fffffff;
@@ -54,11 +58,11 @@ topk_select_kernel(const float* __restrict__ scores, const float* __restrict__ r
     float raw = 0.f, avg = -1.f;
     if (j < M) {
       raw = in[j];
-      if (row_scale) raw = __fdiv_rn(raw, denom);
+      if (row_scale) raw *= inv_total;
       int n = bsz;
       if (j == 0) n -= pad_head;
       if (j == M - 1) n -= pad_tail;
-      avg = __fdiv_rn(raw, static_cast<float>(n));
+      avg = (pow2 && n == bsz) ? raw * inv_bsz : __fdiv_rn(raw, static_cast<float>(n));
       if (!(avg >= 0.f)) avg = 0.f;  // NaN / negative input: rank last among real blocks
     }
     savg[j] = avg;
