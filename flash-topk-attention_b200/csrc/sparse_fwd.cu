@@ -6,16 +6,19 @@
 // One CTA owns 128 consecutive virtual query rows = G q-blocks of one (batch,
 // head) slice and walks the union of their candidate KV blocks in ascending
 // order (see attn_common.cuh).  Roles: warp 0 = TMA producer (Q once, then a
-// ring of K/V block tiles), warp 1 = UMMA issuer, warps 2..5 = 128 softmax
-// threads, one query row each.
+// ring of K/V block tiles), warp 1 = UMMA issuer, warps 2..9 = two softmax
+// groups of 128 threads, one query row per thread in each group.
 //   S = Q K^T      tcgen05 SS, both operands K-major, accumulator in TMEM
-//   P = 2^(c S - m) rounded to the I/O dtype, written back to TMEM
+//   P = 2^(c S - m) rounded to the I/O dtype, written over the S columns
 //   O += P V       tcgen05 with A = P from TMEM, B = V read MN-major from the
 //                  same row-major tile TMA delivered
-// S and P are double buffered so the tensor core computes S of block i+1 while
-// the softmax threads work on block i.  The running maximum is only raised
-// when a block exceeds it by more than 2^8 (P stays inside fp16 range); O is
-// then rescaled in TMEM by its row owner.
+// Even union entries go through S buffer 0 / softmax group 0 / accumulator
+// O0, odd entries through buffer 1 / group 1 / O1, so the two groups work
+// concurrently and the tensor core alternates between them; each group keeps
+// its own running maximum and sum and the two partial results are merged in
+// the epilogue (split-KV merge).  A group raises its running maximum only
+// when a block exceeds it by more than 2^8 (P stays inside fp16 range); its
+// O accumulator is then rescaled in TMEM by the row owners.
 #include <algorithm>
 #include <cmath>
 
@@ -25,11 +28,10 @@
 
 namespace ftk {
 
-constexpr int FW_THREADS = 192;
+constexpr int FW_THREADS = 320;  // 2 + 2 x 4 warps
 constexpr int FW_MAX_STAGES = 4;
-constexpr int FW_COL_S = 0;      // S[2]: 2 x 128 columns
-constexpr int FW_COL_P = 256;    // P[2]: 2 x 64 columns (16-bit pairs)
-constexpr int FW_COL_O = 384;    // O: D columns
+constexpr int FW_COL_S = 0;      // S[2] (P written over them): 2 x 128 columns
+constexpr int FW_COL_O = 256;    // O[2]: 2 x 128 columns
 
 struct FwdParams {
   int N, H, QM, W, Mkv;
@@ -55,9 +57,10 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint8_t* sQ = smem;
   uint8_t* sKV = smem + Q_BYTES;
   __shared__ UnionScratch un;
-  __shared__ __align__(8) uint64_t bars[1 + 2 * FW_MAX_STAGES + 6];
+  __shared__ __align__(8) uint64_t bars[2 + 2 * FW_MAX_STAGES + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
+  __shared__ float s_m[2][128], s_l[2][128];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int m0 = blockIdx.x * p.G;
@@ -70,23 +73,23 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int NST = p.nstages;
 
   const uint32_t bar_q = smem_u32(&bars[0]);
-  auto bar_kvfull = [&](int s) { return smem_u32(&bars[1 + s]); };
-  auto bar_kvempty = [&](int s) { return smem_u32(&bars[1 + FW_MAX_STAGES + s]); };
-  auto bar_sfull = [&](int s) { return smem_u32(&bars[1 + 2 * FW_MAX_STAGES + s]); };
-  auto bar_pfull = [&](int s) { return smem_u32(&bars[1 + 2 * FW_MAX_STAGES + 2 + s]); };
-  auto bar_pvdone = [&](int s) { return smem_u32(&bars[1 + 2 * FW_MAX_STAGES + 4 + s]); };
+  const uint32_t bar_final = smem_u32(&bars[1]);
+  auto bar_kvfull = [&](int s) { return smem_u32(&bars[2 + s]); };
+  auto bar_kvempty = [&](int s) { return smem_u32(&bars[2 + FW_MAX_STAGES + s]); };
+  auto bar_sfull = [&](int s) { return smem_u32(&bars[2 + 2 * FW_MAX_STAGES + s]); };
+  auto bar_pfull = [&](int s) { return smem_u32(&bars[2 + 2 * FW_MAX_STAGES + 2 + s]); };
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(bar_q, 1);
+    mbar_init(bar_final, 1);
     for (int s = 0; s < FW_MAX_STAGES; s++) {
       mbar_init(bar_kvfull(s), 1);
       mbar_init(bar_kvempty(s), 1);
     }
     for (int s = 0; s < 2; s++) {
       mbar_init(bar_sfull(s), 1);
-      mbar_init(bar_pfull(s), 4);  // one arrival per softmax warp
-      mbar_init(bar_pvdone(s), 1);
+      mbar_init(bar_pfull(s), 4);  // one arrival per warp of the owning group
     }
     mbar_init_fence();
     tma_prefetch_desc(&tm_q);
@@ -151,37 +154,41 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (ok && n > 1) ok = issue_s(1);
       for (int i = 0; ok && i < n; i++) {
         const int s = i % NST, sb = i & 1;
-        if (!mbar_wait(bar_pfull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_MMA)) break;
+        if (!mbar_wait(bar_pfull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after();
         const uint32_t vbase = smem_u32(sKV) + s * stage_bytes + NCH * kv_chunk_bytes;
         const int ksteps = p.kvb / 16;
         for (int ks = 0; ks < ksteps; ks++) {
-          umma_ts(tmem + FW_COL_O, tmem + FW_COL_P + sb * 64 + ks * 8,
+          umma_ts(tmem + FW_COL_O + sb * 128, tmem + FW_COL_S + sb * 128 + ks * 8,
                   smem_desc_sw128(vbase + ks * 2048, kv_chunk_bytes, 1024), idesc_pv,
-                  (i > 0) || (ks > 0));
+                  (i >= 2) || (ks > 0));
         }
-        umma_commit(bar_pvdone(sb));
         umma_commit(bar_kvempty(s));
+        // S(i+2) overwrites the columns PV(i) reads P from; the tensor core
+        // runs UMMAs in issue order, so issuing it after PV(i) is enough.
         if (i + 2 < n) ok = issue_s(i + 2);
       }
+      if (ok) umma_commit(bar_final);
     }
   } else {
     // ---------------------------------------------------- softmax threads
+    const int grp_w = (warp - 2) >> 2;       // softmax group = S buffer it drains
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const int grp = r / p.g;
     const int qrow = tile_row0 + r;
     const bool row_valid = (grp < groups) && qrow >= 0 && qrow < p.N;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t s_addr = lane_addr + FW_COL_S + grp_w * 128;
+    const uint32_t o_addr = lane_addr + FW_COL_O + grp_w * 128;
     const float c = p.scale_log2;
     float m_run = -INFINITY, l = 0.f;
     bool ok = true;
 
-    for (int i = 0; ok && i < n; i++) {
-      const int sb = i & 1;
-      if (!mbar_wait(bar_sfull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) { ok = false; break; }
-      if (i >= 2 &&
-          !mbar_wait(bar_pvdone(sb), ((i - 2) >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) {
+    for (int i = grp_w; ok && i < n; i += 2) {
+      // S(i) complete also means PV(i-2) has retired (same issue order), so
+      // this group's O accumulator and P columns are free to touch.
+      if (!mbar_wait(bar_sfull(grp_w), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) {
         ok = false;
         break;
       }
@@ -189,9 +196,80 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const int tok0 = static_cast<int>(un.ids[i]) * p.kvb - p.kv_pad_head;
       const int lo = max(0, -tok0), hi = min(p.kvb, p.N - tok0);
       const bool act = row_valid && ((un.masks[i] >> grp) & 1) && hi > lo;
-      const uint32_t s_addr = lane_addr + FW_COL_S + sb * 128;
-      const uint32_t p_addr = lane_addr + FW_COL_P + sb * 64;
-      if (__any_sync(0xffffffffu, act)) {
+      const bool any_act = __any_sync(0xffffffffu, act);
+      const bool fast = __all_sync(0xffffffffu, act) && lo == 0 && hi == p.kvb;
+
+      if (any_act && p.kvb == 64) {
+        // ---- whole row of S in registers, one TMEM round trip
+        uint32_t v0[32], v1[32];
+        tmem_ld32(s_addr, v0);
+        tmem_ld32(s_addr + 32, v1);
+        tmem_wait_ld();
+        float mt = -INFINITY;
+        if (fast) {
+#pragma unroll
+          for (int x = 0; x < 32; x++)
+            mt = fmaxf(mt, fmaxf(__uint_as_float(v0[x]), __uint_as_float(v1[x])));
+        } else if (act) {
+#pragma unroll
+          for (int x = 0; x < 32; x++) {
+            if (x >= lo && x < hi) mt = fmaxf(mt, __uint_as_float(v0[x]));
+            if (x + 32 >= lo && x + 32 < hi) mt = fmaxf(mt, __uint_as_float(v1[x]));
+          }
+        }
+        const float mt2 = act ? mt * c : -INFINITY;
+        const bool grow = act && (mt2 > m_run + 8.f || m_run == -INFINITY);
+        const float m_new = grow ? mt2 : m_run;
+        const bool resc = grow && l > 0.f;
+        if (__any_sync(0xffffffffu, resc)) {
+          const float alpha = resc ? fast_exp2(m_run - m_new) : 1.f;
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t ov[32];
+            tmem_ld32(o_addr + c0, ov);
+            tmem_wait_ld();
+#pragma unroll
+            for (int x = 0; x < 32; x++) ov[x] = __float_as_uint(__uint_as_float(ov[x]) * alpha);
+            tmem_st32(o_addr + c0, ov);
+          }
+          l *= alpha;
+        }
+        m_run = m_new;
+        uint32_t pk[32];
+        float l0 = 0.f, l1 = 0.f;
+        if (fast) {
+#pragma unroll
+          for (int x = 0; x < 32; x += 2) {
+            const float a0 = fast_exp2(fmaf(__uint_as_float(v0[x]), c, -m_run));
+            const float a1 = fast_exp2(fmaf(__uint_as_float(v0[x + 1]), c, -m_run));
+            const float b0 = fast_exp2(fmaf(__uint_as_float(v1[x]), c, -m_run));
+            const float b1 = fast_exp2(fmaf(__uint_as_float(v1[x + 1]), c, -m_run));
+            l0 += a0 + a1;
+            l1 += b0 + b1;
+            pk[x >> 1] = pack2(a0, a1, p.fmt);
+            pk[16 + (x >> 1)] = pack2(b0, b1, p.fmt);
+          }
+        } else {
+#pragma unroll
+          for (int x = 0; x < 32; x += 2) {
+            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+            if (act && x >= lo && x < hi) a0 = fast_exp2(fmaf(__uint_as_float(v0[x]), c, -m_run));
+            if (act && x + 1 >= lo && x + 1 < hi)
+              a1 = fast_exp2(fmaf(__uint_as_float(v0[x + 1]), c, -m_run));
+            if (act && x + 32 >= lo && x + 32 < hi)
+              b0 = fast_exp2(fmaf(__uint_as_float(v1[x]), c, -m_run));
+            if (act && x + 33 >= lo && x + 33 < hi)
+              b1 = fast_exp2(fmaf(__uint_as_float(v1[x + 1]), c, -m_run));
+            l0 += a0 + a1;
+            l1 += b0 + b1;
+            pk[x >> 1] = pack2(a0, a1, p.fmt);
+            pk[16 + (x >> 1)] = pack2(b0, b1, p.fmt);
+          }
+        }
+        l += l0 + l1;
+        tmem_st32(s_addr, pk);
+      } else if (any_act) {
+        // ---- generic block size: two passes over S in 16-column chunks.  P
+        // chunk k lands on columns S has already been read from.
         float mt = -INFINITY;
         for (int c0 = 0; c0 < p.kvb; c0 += 16) {
           uint32_t v[16];
@@ -206,23 +284,15 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const float m_new = grow ? mt2 : m_run;
         const bool resc = grow && l > 0.f;
         if (__any_sync(0xffffffffu, resc)) {
-          // O is only safe to touch once every PV issued so far has retired
-          if (!mbar_wait(bar_pvdone((i - 1) & 1), ((i - 1) >> 1) & 1, w,
-                         FTK_DEV_TIMEOUT_CONSUMER)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
           const float alpha = resc ? fast_exp2(m_run - m_new) : 1.f;
           for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t v[32];
-            tmem_ld32(lane_addr + FW_COL_O + c0, v);
+            uint32_t ov[32];
+            tmem_ld32(o_addr + c0, ov);
             tmem_wait_ld();
 #pragma unroll
-            for (int x = 0; x < 32; x++) v[x] = __float_as_uint(__uint_as_float(v[x]) * alpha);
-            tmem_st32(lane_addr + FW_COL_O + c0, v);
+            for (int x = 0; x < 32; x++) ov[x] = __float_as_uint(__uint_as_float(ov[x]) * alpha);
+            tmem_st32(o_addr + c0, ov);
           }
-          tmem_wait_st();
           l *= alpha;
         }
         m_run = m_new;
@@ -241,44 +311,62 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             l += p0 + p1;
             pk[x >> 1] = pack2(p0, p1, p.fmt);
           }
-          tmem_st8(p_addr + (c0 >> 1), pk);
+          tmem_st8(s_addr + (c0 >> 1), pk);
         }
       } else {
         uint32_t z[8];
 #pragma unroll
         for (int x = 0; x < 8; x++) z[x] = 0u;
-        for (int c0 = 0; c0 < p.kvb; c0 += 16) tmem_st8(p_addr + (c0 >> 1), z);
+        for (int c0 = 0; c0 < p.kvb; c0 += 16) tmem_st8(s_addr + (c0 >> 1), z);
       }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pfull(sb));
+      if (lane == 0) mbar_arrive(bar_pfull(grp_w));
     }
 
     // ------------------------------------------------------------ epilogue
-    if (ok && n > 0)
-      ok = mbar_wait(bar_pvdone((n - 1) & 1), ((n - 1) >> 1) & 1, w, FTK_DEV_TIMEOUT_EPILOGUE);
+    // merge the two groups' partial softmax states, then each group converts
+    // and stores one half of the head dimension
+    s_m[grp_w][r] = m_run;
+    s_l[grp_w][r] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (ok && n > 0) ok = mbar_wait(bar_final, 0, w, FTK_DEV_TIMEOUT_EPILOGUE);
     if (ok) {
       tc_fence_after();
-      const bool have = (n > 0) && l > 0.f;
-      const float inv = have ? 1.f / l : 0.f;
+      const float ma = s_m[0][r], mb = s_m[1][r];
+      const float la = s_l[0][r], lb = s_l[1][r];
+      const float mm = fmaxf(ma, mb);
+      const float fa = la > 0.f ? fast_exp2(ma - mm) : 0.f;
+      const float fb = lb > 0.f ? fast_exp2(mb - mm) : 0.f;
+      const float lt = la * fa + lb * fb;
+      const bool have = (n > 0) && lt > 0.f;
+      const float inv = have ? 1.f / lt : 0.f;
+      const float wa = fa * inv, wb = fb * inv;
       uint8_t* orow = nullptr;
       if (row_valid)
         orow = static_cast<uint8_t*>(p.o) +
                2 * (static_cast<int64_t>(b_idx) * p.so_b + static_cast<int64_t>(qrow) * p.so_n +
                     static_cast<int64_t>(h_idx) * p.so_h);
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t v[32];
-        if (n > 0) {
-          tmem_ld32(lane_addr + FW_COL_O + c0, v);
-          tmem_wait_ld();
-        }
+      constexpr int HALF = D / 2;
+      for (int c0 = grp_w * HALF; c0 < (grp_w + 1) * HALF; c0 += 32) {
+        uint32_t va[32], vb[32];
+        if (n > 0) tmem_ld32(lane_addr + FW_COL_O + c0, va);
+        if (n > 1) tmem_ld32(lane_addr + FW_COL_O + 128 + c0, vb);
+        if (n > 0) tmem_wait_ld();
         if (row_valid) {
           uint32_t pk[16];
 #pragma unroll
           for (int x = 0; x < 32; x += 2) {
-            const float a = have ? __uint_as_float(v[x]) * inv : 0.f;
-            const float b = have ? __uint_as_float(v[x + 1]) * inv : 0.f;
+            float a = 0.f, b = 0.f;
+            if (have) {
+              a = __uint_as_float(va[x]) * wa;
+              b = __uint_as_float(va[x + 1]) * wa;
+              if (n > 1) {
+                a = fmaf(__uint_as_float(vb[x]), wb, a);
+                b = fmaf(__uint_as_float(vb[x + 1]), wb, b);
+              }
+            }
             pk[x >> 1] = pack2(a, b, p.fmt);
           }
           uint4* dst = reinterpret_cast<uint4*>(orow + c0 * 2);
@@ -287,9 +375,9 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             dst[x] = make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]);
         }
       }
-      if (row_valid)
+      if (row_valid && grp_w == 0)
         p.lse[static_cast<int64_t>(bh) * p.N + qrow] =
-            have ? (m_run + log2f(l)) * 0.6931471805599453f : -INFINITY;
+            have ? (mm + log2f(lt)) * 0.6931471805599453f : -INFINITY;
     }
   }
 
