@@ -76,11 +76,13 @@ __device__ __forceinline__ TileInfo tile_info(const ScoreParams& p, int t) {
   return ti;
 }
 
-// Which softmax group drains tile t.  Tiles alternate between the two groups;
-// when a score block spans several tiles all of them go to one group so that
-// every block sum is produced by a single thread.
+// Which softmax group drains tile t.  Tiles alternate between the two groups,
+// each group bound to one accumulator stage, so a group meets every phase of
+// its stage's barriers in order (a one-bit parity wait must never skip a
+// phase).  When a score block spans several tiles (block size > 128) one
+// thread has to see all of them, and group 0 takes every tile.
 __device__ __forceinline__ int tile_owner(const ScoreParams& p, int t) {
-  return (p.tiles_per_block > 1 ? t / p.tiles_per_block : t) & 1;
+  return p.tiles_per_block > 1 ? 0 : (t & 1);
 }
 
 template <int D>

@@ -47,7 +47,7 @@ __global__ void delta_kernel(const uint8_t* __restrict__ o, const uint8_t* __res
   if (lane == 0) delta[(b * H + h) * N + n] = acc;
 }
 
-constexpr int BW_THREADS = 192;
+constexpr int BW_THREADS = 320;  // 2 + 2 x 4 warps
 constexpr int BW_MAX_STAGES = 4;
 
 struct BwdParams {
@@ -101,7 +101,8 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
   auto bar_kvempty = [&](int s) { return smem_u32(&bars[1 + BW_MAX_STAGES + s]); };
   auto bar_afull = [&](int s) { return smem_u32(&bars[1 + 2 * BW_MAX_STAGES + s]); };
   auto bar_dsfull = [&](int s) { return smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 2 + s]); };
-  auto bar_bdone = [&](int s) { return smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 4 + s]); };
+  // arrives once, after the last UMMA of the CTA has retired
+  const uint32_t bar_final = smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 4]);
 
   if (tid == 0) {
     abort_flag = 0;
@@ -113,8 +114,8 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
     for (int s = 0; s < 2; s++) {
       mbar_init(bar_afull(s), 1);
       mbar_init(bar_dsfull(s), 4);
-      mbar_init(bar_bdone(s), 1);
     }
+    mbar_init(bar_final, 1);
     mbar_init_fence();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_do);
@@ -193,18 +194,23 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
           umma_ts(tmem + 384, tmem + 256 + sb * 32 + ks * 8,
                   smem_desc_sw128(kbase + ks * 2048, kv_chunk_bytes, 1024), idesc_b,
                   (i > 0) || (ks > 0));
-        umma_commit(bar_bdone(sb));
         umma_commit(bar_kvempty(s));
         if (i + 2 < n) ok = issue_a(i + 2);
       }
+      if (ok) umma_commit(bar_final);
     }
   } else {
+    // two groups of 128 threads; group w drains the buffers of tiles i = w (mod 2)
+    const int wg = (warp - 2) >> 2;
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const int grp = r / p.g;
     const int qrow = tile_row0 + r;
     const bool row_valid = (grp < groups) && qrow >= 0 && qrow < p.N;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t s_addr = lane_addr + wg * 64;
+    const uint32_t dp_addr = lane_addr + 128 + wg * 64;
+    const uint32_t ds_addr = lane_addr + 256 + wg * 32;
     const float c = p.scale_log2;
     float lse2 = 0.f, dl = 0.f;
     if (row_valid) {
@@ -212,10 +218,10 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       dl = p.delta[static_cast<int64_t>(bh) * p.N + qrow];
     }
     bool ok = true;
-    for (int i = 0; ok && i < n; i++) {
-      const int sb = i & 1;
-      if (!mbar_wait(bar_afull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) { ok = false; break; }
-      if (i >= 2 && !mbar_wait(bar_bdone(sb), ((i - 2) >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) {
+    for (int i = wg; ok && i < n; i += 2) {
+      // A(i) complete also means B(i-2) has retired (same issue order), so the
+      // dS columns of this buffer are free again.
+      if (!mbar_wait(bar_afull(wg), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) {
         ok = false;
         break;
       }
@@ -223,33 +229,62 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       const int tok0 = static_cast<int>(un.ids[i]) * p.kvb - p.kv_pad_head;
       const int lo = max(0, -tok0), hi = min(p.kvb, p.N - tok0);
       const bool act = row_valid && ((un.masks[i] >> grp) & 1) && hi > lo;
-      for (int c0 = 0; c0 < p.kvb; c0 += 16) {
-        uint32_t sv[16], dv[16], pk[8];
-        tmem_ld16(lane_addr + sb * 64 + c0, sv);
-        tmem_ld16(lane_addr + 128 + sb * 64 + c0, dv);
-        tmem_wait_ld();
+      const bool fast = __all_sync(0xffffffffu, act) && lo == 0 && hi == p.kvb;
+      for (int c0 = 0; c0 < p.kvb; c0 += 32) {
+        if (p.kvb - c0 >= 32) {
+          uint32_t sv[32], dv[32], pk[16];
+          tmem_ld32(s_addr + c0, sv);
+          tmem_ld32(dp_addr + c0, dv);
+          tmem_wait_ld();
+          if (fast) {
 #pragma unroll
-        for (int x = 0; x < 16; x += 2) {
-          float d0 = 0.f, d1 = 0.f;
-          if (act && c0 + x >= lo && c0 + x < hi) {
-            const float pr = fast_exp2(fmaf(__uint_as_float(sv[x]), c, -lse2));
-            d0 = pr * (__uint_as_float(dv[x]) - dl);
+            for (int x = 0; x < 32; x += 2) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(sv[x]), c, -lse2));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(sv[x + 1]), c, -lse2));
+              pk[x >> 1] = pack2(p0 * (__uint_as_float(dv[x]) - dl),
+                                 p1 * (__uint_as_float(dv[x + 1]) - dl), p.fmt);
+            }
+          } else {
+#pragma unroll
+            for (int x = 0; x < 32; x += 2) {
+              float d0 = 0.f, d1 = 0.f;
+              if (act && c0 + x >= lo && c0 + x < hi)
+                d0 = fast_exp2(fmaf(__uint_as_float(sv[x]), c, -lse2)) *
+                     (__uint_as_float(dv[x]) - dl);
+              if (act && c0 + x + 1 >= lo && c0 + x + 1 < hi)
+                d1 = fast_exp2(fmaf(__uint_as_float(sv[x + 1]), c, -lse2)) *
+                     (__uint_as_float(dv[x + 1]) - dl);
+              pk[x >> 1] = pack2(d0, d1, p.fmt);
+            }
           }
-          if (act && c0 + x + 1 >= lo && c0 + x + 1 < hi) {
-            const float pr = fast_exp2(fmaf(__uint_as_float(sv[x + 1]), c, -lse2));
-            d1 = pr * (__uint_as_float(dv[x + 1]) - dl);
+          tmem_st16(ds_addr + (c0 >> 1), pk);
+        } else {
+          uint32_t sv[16], dv[16], pk[8];
+          tmem_ld16(s_addr + c0, sv);
+          tmem_ld16(dp_addr + c0, dv);
+          tmem_wait_ld();
+#pragma unroll
+          for (int x = 0; x < 16; x += 2) {
+            float d0 = 0.f, d1 = 0.f;
+            if (act && c0 + x >= lo && c0 + x < hi)
+              d0 = fast_exp2(fmaf(__uint_as_float(sv[x]), c, -lse2)) *
+                   (__uint_as_float(dv[x]) - dl);
+            if (act && c0 + x + 1 >= lo && c0 + x + 1 < hi)
+              d1 = fast_exp2(fmaf(__uint_as_float(sv[x + 1]), c, -lse2)) *
+                   (__uint_as_float(dv[x + 1]) - dl);
+            pk[x >> 1] = pack2(d0, d1, p.fmt);
           }
-          pk[x >> 1] = pack2(d0, d1, p.fmt);
+          tmem_st8(ds_addr + (c0 >> 1), pk);
         }
-        tmem_st8(lane_addr + 256 + sb * 32 + (c0 >> 1), pk);
       }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_dsfull(sb));
+      if (lane == 0) mbar_arrive(bar_dsfull(wg));
     }
+    // epilogue: each group converts and stores one half of the head dimension
     if (ok && n > 0)
-      ok = mbar_wait(bar_bdone((n - 1) & 1), ((n - 1) >> 1) & 1, w, FTK_DEV_TIMEOUT_EPILOGUE);
+      ok = mbar_wait(bar_final, 0, w, FTK_DEV_TIMEOUT_EPILOGUE);
     if (ok) {
       tc_fence_after();
       uint8_t* orow = nullptr;
@@ -257,7 +292,8 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
         orow = static_cast<uint8_t*>(p.out0) +
                2 * (static_cast<int64_t>(b_idx) * p.s0_b + static_cast<int64_t>(qrow) * p.s0_n +
                     static_cast<int64_t>(h_idx) * p.s0_h);
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      constexpr int HALF = D / 2;
+      for (int c0 = wg * HALF; c0 < (wg + 1) * HALF; c0 += 32) {
         uint32_t v[32];
         if (n > 0) {
           tmem_ld32(lane_addr + 384 + c0, v);
@@ -307,7 +343,7 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
   __shared__ __align__(8) uint64_t bars[1 + 2 * BW_MAX_STAGES + 6];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
-  __shared__ float s_lse2[2][128], s_delta[2][128];
+  __shared__ __align__(16) float s_lse2[2][2][128], s_delta[2][2][128];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int j0 = blockIdx.x * p.G;          // first kv block of the tile
@@ -324,7 +360,8 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
   auto bar_qempty = [&](int s) { return smem_u32(&bars[1 + BW_MAX_STAGES + s]); };
   auto bar_afull = [&](int s) { return smem_u32(&bars[1 + 2 * BW_MAX_STAGES + s]); };
   auto bar_pfull = [&](int s) { return smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 2 + s]); };
-  auto bar_bdone = [&](int s) { return smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 4 + s]); };
+  // arrives once, after the last UMMA of the CTA has retired
+  const uint32_t bar_final = smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 4]);
 
   if (tid == 0) {
     abort_flag = 0;
@@ -336,8 +373,8 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
     for (int s = 0; s < 2; s++) {
       mbar_init(bar_afull(s), 1);
       mbar_init(bar_pfull(s), 4);
-      mbar_init(bar_bdone(s), 1);
     }
+    mbar_init(bar_final, 1);
     mbar_init_fence();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_do);
@@ -421,26 +458,30 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
           umma_ts(tmem + 384, tmem + 128 + sb * 64 + ks * 8,
                   smem_desc_sw128(qbase + ks * 2048, q_chunk_bytes, 1024), idesc_b, acc);
         }
-        umma_commit(bar_bdone(sb));
         umma_commit(bar_qempty(s));
         if (i + 2 < n) ok = issue_a(i + 2);
       }
+      if (ok) umma_commit(bar_final);
     }
   } else {
+    // two groups of 128 threads; group w drains the buffers of tiles i = w (mod 2)
+    const int wg = (warp - 2) >> 2;
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
-    const int ct = tid - 64;                 // 0..127 among the compute threads
+    const int ct = (tid - 64) & 127;         // index inside the group
     const int grp = r / p.kvb;
     const int tok = tile_tok0 + r;
     const bool row_valid = (grp < groups) && tok >= 0 && tok < p.N;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t st_addr = lane_addr + wg * 64;         // S^T, then P^T
+    const uint32_t dp_addr = lane_addr + 128 + wg * 64;   // dP^T, then dS^T
     const float c = p.scale_log2;
     bool ok = true;
-    // every compute thread runs all n rounds (the named barrier below needs
-    // all 128 of them); after a failed wait a thread only keeps the barrier
-    // company and does no more work.
-    for (int i = 0; i < n; i++) {
-      const int sb = i & 1;
+    // every thread of a group runs all of the group's rounds (its named
+    // barrier needs all 128); after a failed wait a thread only keeps the
+    // barrier company and does no more work.
+    for (int i = wg; i < n; i += 2) {
+      const int pb = (i >> 1) & 1;           // per-group double buffer of lse / delta
       const int row0 = static_cast<int>(un.ids[i]) * p.g - p.q_pad_head;
       if (ct < p.g) {
         const int t = row0 + ct;
@@ -449,79 +490,88 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
           l2 = p.lse[static_cast<int64_t>(bh) * p.N + t] * 1.4426950408889634f;
           dl = p.delta[static_cast<int64_t>(bh) * p.N + t];
         }
-        s_lse2[sb][ct] = l2;
-        s_delta[sb][ct] = dl;
+        s_lse2[wg][pb][ct] = l2;
+        s_delta[wg][pb][ct] = dl;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (wg == 0)
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      else
+        asm volatile("bar.sync 2, 128;" ::: "memory");
       if (!ok) continue;
-      if (!mbar_wait(bar_afull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) {
+      if (!mbar_wait(bar_afull(wg), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) {
         ok = false;
         continue;
       }
       tc_fence_after();
       const int lo = max(0, -row0), hi = min(p.g, p.N - row0);
       const bool act = row_valid && ((un.masks[i] >> grp) & 1) && hi > lo;
+      const bool fast = __all_sync(0xffffffffu, act) && lo == 0 && hi == p.g;
+      const float4* l4 = reinterpret_cast<const float4*>(s_lse2[wg][pb]);
+      const float4* d4 = reinterpret_cast<const float4*>(s_delta[wg][pb]);
       for (int c0 = 0; c0 < p.g; c0 += 16) {
         uint32_t sv[16], dv[16], pp[8], pd[8];
-        tmem_ld16(lane_addr + sb * 64 + c0, sv);
-        tmem_ld16(lane_addr + 128 + sb * 64 + c0, dv);
+        tmem_ld16(st_addr + c0, sv);
+        tmem_ld16(dp_addr + c0, dv);
         tmem_wait_ld();
 #pragma unroll
-        for (int x = 0; x < 16; x += 2) {
-          float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
-          if (act && c0 + x >= lo && c0 + x < hi) {
-            p0 = fast_exp2(fmaf(__uint_as_float(sv[x]), c, -s_lse2[sb][c0 + x]));
-            d0 = p0 * (__uint_as_float(dv[x]) - s_delta[sb][c0 + x]);
+        for (int x = 0; x < 16; x += 4) {
+          const float4 lq = l4[(c0 + x) >> 2];
+          const float4 dq = d4[(c0 + x) >> 2];
+          const float ls[4] = {lq.x, lq.y, lq.z, lq.w};
+          const float ds[4] = {dq.x, dq.y, dq.z, dq.w};
+          float pv[4], dsv[4];
+#pragma unroll
+          for (int y = 0; y < 4; y++) {
+            const bool on = fast || (act && c0 + x + y >= lo && c0 + x + y < hi);
+            const float pr = on ? fast_exp2(fmaf(__uint_as_float(sv[x + y]), c, -ls[y])) : 0.f;
+            pv[y] = pr;
+            dsv[y] = pr * (__uint_as_float(dv[x + y]) - ds[y]);
           }
-          if (act && c0 + x + 1 >= lo && c0 + x + 1 < hi) {
-            p1 = fast_exp2(fmaf(__uint_as_float(sv[x + 1]), c, -s_lse2[sb][c0 + x + 1]));
-            d1 = p1 * (__uint_as_float(dv[x + 1]) - s_delta[sb][c0 + x + 1]);
-          }
-          pp[x >> 1] = pack2(p0, p1, p.fmt);
-          pd[x >> 1] = pack2(d0, d1, p.fmt);
+          pp[x >> 1] = pack2(pv[0], pv[1], p.fmt);
+          pp[(x >> 1) + 1] = pack2(pv[2], pv[3], p.fmt);
+          pd[x >> 1] = pack2(dsv[0], dsv[1], p.fmt);
+          pd[(x >> 1) + 1] = pack2(dsv[2], dsv[3], p.fmt);
         }
-        tmem_st8(lane_addr + sb * 64 + (c0 >> 1), pp);
-        tmem_st8(lane_addr + 128 + sb * 64 + (c0 >> 1), pd);
+        tmem_st8(st_addr + (c0 >> 1), pp);
+        tmem_st8(dp_addr + (c0 >> 1), pd);
       }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pfull(sb));
+      if (lane == 0) mbar_arrive(bar_pfull(wg));
     }
     if (ok && n > 0)
-      ok = mbar_wait(bar_bdone((n - 1) & 1), ((n - 1) >> 1) & 1, w, FTK_DEV_TIMEOUT_EPILOGUE);
+      ok = mbar_wait(bar_final, 0, w, FTK_DEV_TIMEOUT_EPILOGUE);
     if (ok) {
       tc_fence_after();
+      // group 0 stores dV (TMEM 256..), group 1 stores dK (TMEM 384.., scaled)
+      const int which = wg;
+      uint8_t* base = static_cast<uint8_t*>(which == 0 ? p.out1 : p.out0);
+      const int64_t sb_ = which == 0 ? p.s1_b : p.s0_b, sn_ = which == 0 ? p.s1_n : p.s0_n,
+                    sh_ = which == 0 ? p.s1_h : p.s0_h;
+      const float mul = which == 0 ? 1.f : p.scale;
+      uint8_t* orow = nullptr;
+      if (row_valid)
+        orow = base + 2 * (static_cast<int64_t>(b_idx) * sb_ + static_cast<int64_t>(tok) * sn_ +
+                           static_cast<int64_t>(h_idx) * sh_);
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t v[32];
+        if (n > 0) {
+          tmem_ld32(lane_addr + 256 + which * 128 + c0, v);
+          tmem_wait_ld();
+        }
+        if (row_valid) {
+          uint32_t pk[16];
 #pragma unroll
-      for (int which = 0; which < 2; which++) {
-        // which 0: dV (TMEM 256) -> out1 ; which 1: dK (TMEM 384, scaled) -> out0
-        uint8_t* base = static_cast<uint8_t*>(which == 0 ? p.out1 : p.out0);
-        const int64_t sb_ = which == 0 ? p.s1_b : p.s0_b, sn_ = which == 0 ? p.s1_n : p.s0_n,
-                      sh_ = which == 0 ? p.s1_h : p.s0_h;
-        const float mul = which == 0 ? 1.f : p.scale;
-        uint8_t* orow = nullptr;
-        if (row_valid)
-          orow = base + 2 * (static_cast<int64_t>(b_idx) * sb_ + static_cast<int64_t>(tok) * sn_ +
-                             static_cast<int64_t>(h_idx) * sh_);
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t v[32];
-          if (n > 0) {
-            tmem_ld32(lane_addr + 256 + which * 128 + c0, v);
-            tmem_wait_ld();
+          for (int x = 0; x < 32; x += 2) {
+            const float a = n > 0 ? __uint_as_float(v[x]) * mul : 0.f;
+            const float b = n > 0 ? __uint_as_float(v[x + 1]) * mul : 0.f;
+            pk[x >> 1] = pack2(a, b, p.fmt);
           }
-          if (row_valid) {
-            uint32_t pk[16];
+          uint4* dst = reinterpret_cast<uint4*>(orow + c0 * 2);
 #pragma unroll
-            for (int x = 0; x < 32; x += 2) {
-              const float a = n > 0 ? __uint_as_float(v[x]) * mul : 0.f;
-              const float b = n > 0 ? __uint_as_float(v[x + 1]) * mul : 0.f;
-              pk[x >> 1] = pack2(a, b, p.fmt);
-            }
-            uint4* dst = reinterpret_cast<uint4*>(orow + c0 * 2);
-#pragma unroll
-            for (int x = 0; x < 4; x++)
-              dst[x] = make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]);
-          }
+          for (int x = 0; x < 4; x++)
+            dst[x] = make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]);
         }
       }
     }
