@@ -231,6 +231,14 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
   return d;
 }
 
+// Same descriptor, start address moved by `byte_off` (a multiple of 16; the
+// address field is the low 14 bits and shared memory is < 256 KB, so the sum
+// never carries into the other fields).  Lets a kernel build each tile's base
+// descriptor once and step through it with one add per UMMA.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t byte_off) {
+  return desc + static_cast<uint64_t>(byte_off >> 4);
+}
+
 // Instruction descriptor for kind::f16 with fp32 accumulation.
 //   ab_fmt: 0 = fp16, 1 = bf16; *_mn = 1 when that operand is MN-major.
 __host__ __device__ constexpr uint32_t umma_idesc(int m, int n, int ab_fmt, int a_mn, int b_mn) {

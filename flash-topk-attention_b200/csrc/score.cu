@@ -172,6 +172,8 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     // -------------------------------------------------------- UMMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(128, SC_KT, p.fmt, 0, 0);
+      const uint64_t qdesc0 = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+      const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sK), 16, 1024);
       bool ok = mbar_wait(bar_q, 0, w, FTK_DEV_TIMEOUT_MMA);
       for (int t = 0; ok && t < T; t++) {
         const int s = t % SC_STAGES;
@@ -181,16 +183,15 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
         if (!mbar_wait(bar_aempty(a), pa ^ 1, w, FTK_DEV_TIMEOUT_MMA)) break;
         if (!mbar_wait(bar_kfull(s), ph, w, FTK_DEV_TIMEOUT_MMA)) break;
         tc_fence_after();
-        const uint32_t kbase = smem_u32(sK) + s * K_STAGE_BYTES;
+        const uint64_t kdesc = desc_advance(kdesc0, s * K_STAGE_BYTES);
 #pragma unroll
         for (int half = 0; half < 2; half++) {
           const uint32_t d_tmem = tmem + static_cast<uint32_t>((a * 2 + half) * SC_KT);
-          const uint32_t qbase = smem_u32(sQ) + half * NCH * SC_CHUNK_BYTES;
+          const uint64_t qdesc = desc_advance(qdesc0, half * NCH * SC_CHUNK_BYTES);
 #pragma unroll
           for (int ks = 0; ks < D / 16; ks++) {
             const uint32_t off = (ks / 4) * SC_CHUNK_BYTES + (ks % 4) * 32;
-            umma_ss(d_tmem, smem_desc_sw128(qbase + off, 16, 1024),
-                    smem_desc_sw128(kbase + off, 16, 1024), idesc, ks > 0);
+            umma_ss(d_tmem, desc_advance(qdesc, off), desc_advance(kdesc, off), idesc, ks > 0);
           }
         }
         umma_commit(bar_kempty(s));  // smem stage reusable once these UMMAs retire

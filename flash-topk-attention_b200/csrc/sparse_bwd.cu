@@ -158,27 +158,31 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
     if (lane == 0 && n > 0) {
       const uint32_t idesc_a = umma_idesc(128, p.kvb, p.fmt, 0, 0);
       const uint32_t idesc_b = umma_idesc(128, D, p.fmt, 0, 1);
+      const uint64_t qdesc0 = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+      const uint64_t dodesc0 = smem_desc_sw128(smem_u32(sDO), 16, 1024);
+      const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sKV), 16, 1024);
+      const uint64_t kmn0 = smem_desc_sw128(smem_u32(sKV), kv_chunk_bytes, 1024);
       bool ok = mbar_wait(bar_q, 0, w, FTK_DEV_TIMEOUT_MMA);
       auto issue_a = [&](int i) -> bool {
         const int s = i % NST;
         if (!mbar_wait(bar_kvfull(s), (i / NST) & 1, w, FTK_DEV_TIMEOUT_MMA)) return false;
         tc_fence_after();
-        const uint32_t kbase = smem_u32(sKV) + s * stage_bytes;
-        const uint32_t vbase = kbase + NCH * kv_chunk_bytes;
+        const uint64_t kdesc = desc_advance(kdesc0, s * stage_bytes);
+        const uint64_t vdesc = desc_advance(kdesc, NCH * kv_chunk_bytes);
         const uint32_t sb = i & 1;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ks++) {
           const uint32_t qoff = (ks / 4) * 128 * 128 + (ks % 4) * 32;
           const uint32_t koff = (ks / 4) * kv_chunk_bytes + (ks % 4) * 32;
-          umma_ss(tmem + sb * 64, smem_desc_sw128(smem_u32(sQ) + qoff, 16, 1024),
-                  smem_desc_sw128(kbase + koff, 16, 1024), idesc_a, ks > 0);
+          umma_ss(tmem + sb * 64, desc_advance(qdesc0, qoff), desc_advance(kdesc, koff), idesc_a,
+                  ks > 0);
         }
 #pragma unroll
         for (int ks = 0; ks < D / 16; ks++) {
           const uint32_t qoff = (ks / 4) * 128 * 128 + (ks % 4) * 32;
           const uint32_t koff = (ks / 4) * kv_chunk_bytes + (ks % 4) * 32;
-          umma_ss(tmem + 128 + sb * 64, smem_desc_sw128(smem_u32(sDO) + qoff, 16, 1024),
-                  smem_desc_sw128(vbase + koff, 16, 1024), idesc_a, ks > 0);
+          umma_ss(tmem + 128 + sb * 64, desc_advance(dodesc0, qoff), desc_advance(vdesc, koff),
+                  idesc_a, ks > 0);
         }
         umma_commit(bar_afull(sb));
         return true;
@@ -189,11 +193,10 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
         const int s = i % NST, sb = i & 1;
         if (!mbar_wait(bar_dsfull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_MMA)) break;
         tc_fence_after();
-        const uint32_t kbase = smem_u32(sKV) + s * stage_bytes;
+        const uint64_t kmn = desc_advance(kmn0, s * stage_bytes);
         for (int ks = 0; ks < p.kvb / 16; ks++)
-          umma_ts(tmem + 384, tmem + 256 + sb * 32 + ks * 8,
-                  smem_desc_sw128(kbase + ks * 2048, kv_chunk_bytes, 1024), idesc_b,
-                  (i > 0) || (ks > 0));
+          umma_ts(tmem + 384, tmem + 256 + sb * 32 + ks * 8, desc_advance(kmn, ks * 2048),
+                  idesc_b, (i > 0) || (ks > 0));
         umma_commit(bar_kvempty(s));
         if (i + 2 < n) ok = issue_a(i + 2);
       }
@@ -418,27 +421,31 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
     if (lane == 0 && n > 0) {
       const uint32_t idesc_a = umma_idesc(128, p.g, p.fmt, 0, 0);
       const uint32_t idesc_b = umma_idesc(128, D, p.fmt, 0, 1);
+      const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sK), 16, 1024);
+      const uint64_t vdesc0 = smem_desc_sw128(smem_u32(sV), 16, 1024);
+      const uint64_t qdesc0 = smem_desc_sw128(smem_u32(sQD), 16, 1024);
+      const uint64_t qmn0 = smem_desc_sw128(smem_u32(sQD), q_chunk_bytes, 1024);
       bool ok = mbar_wait(bar_kv, 0, w, FTK_DEV_TIMEOUT_MMA);
       auto issue_a = [&](int i) -> bool {
         const int s = i % NST;
         if (!mbar_wait(bar_qfull(s), (i / NST) & 1, w, FTK_DEV_TIMEOUT_MMA)) return false;
         tc_fence_after();
-        const uint32_t qbase = smem_u32(sQD) + s * stage_bytes;
-        const uint32_t dobase = qbase + NCH * q_chunk_bytes;
+        const uint64_t qdesc = desc_advance(qdesc0, s * stage_bytes);
+        const uint64_t dodesc = desc_advance(qdesc, NCH * q_chunk_bytes);
         const uint32_t sb = i & 1;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ks++) {
           const uint32_t aoff = (ks / 4) * 128 * 128 + (ks % 4) * 32;
           const uint32_t boff = (ks / 4) * q_chunk_bytes + (ks % 4) * 32;
-          umma_ss(tmem + sb * 64, smem_desc_sw128(smem_u32(sK) + aoff, 16, 1024),
-                  smem_desc_sw128(qbase + boff, 16, 1024), idesc_a, ks > 0);
+          umma_ss(tmem + sb * 64, desc_advance(kdesc0, aoff), desc_advance(qdesc, boff), idesc_a,
+                  ks > 0);
         }
 #pragma unroll
         for (int ks = 0; ks < D / 16; ks++) {
           const uint32_t aoff = (ks / 4) * 128 * 128 + (ks % 4) * 32;
           const uint32_t boff = (ks / 4) * q_chunk_bytes + (ks % 4) * 32;
-          umma_ss(tmem + 128 + sb * 64, smem_desc_sw128(smem_u32(sV) + aoff, 16, 1024),
-                  smem_desc_sw128(dobase + boff, 16, 1024), idesc_a, ks > 0);
+          umma_ss(tmem + 128 + sb * 64, desc_advance(vdesc0, aoff), desc_advance(dodesc, boff),
+                  idesc_a, ks > 0);
         }
         umma_commit(bar_afull(sb));
         return true;
@@ -449,14 +456,13 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
         const int s = i % NST, sb = i & 1;
         if (!mbar_wait(bar_pfull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_MMA)) break;
         tc_fence_after();
-        const uint32_t qbase = smem_u32(sQD) + s * stage_bytes;
-        const uint32_t dobase = qbase + NCH * q_chunk_bytes;
+        const uint64_t qmn = desc_advance(qmn0, s * stage_bytes);
+        const uint64_t domn = desc_advance(qmn, NCH * q_chunk_bytes);
         for (int ks = 0; ks < p.g / 16; ks++) {
           const bool acc = (i > 0) || (ks > 0);
-          umma_ts(tmem + 256, tmem + sb * 64 + ks * 8,
-                  smem_desc_sw128(dobase + ks * 2048, q_chunk_bytes, 1024), idesc_b, acc);
-          umma_ts(tmem + 384, tmem + 128 + sb * 64 + ks * 8,
-                  smem_desc_sw128(qbase + ks * 2048, q_chunk_bytes, 1024), idesc_b, acc);
+          umma_ts(tmem + 256, tmem + sb * 64 + ks * 8, desc_advance(domn, ks * 2048), idesc_b, acc);
+          umma_ts(tmem + 384, tmem + 128 + sb * 64 + ks * 8, desc_advance(qmn, ks * 2048), idesc_b,
+                  acc);
         }
         umma_commit(bar_qempty(s));
         if (i + 2 < n) ok = issue_a(i + 2);

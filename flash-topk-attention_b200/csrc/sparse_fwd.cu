@@ -133,19 +133,21 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (lane == 0 && n > 0) {
       const uint32_t idesc_s = umma_idesc(128, p.kvb, p.fmt, 0, 0);
       const uint32_t idesc_pv = umma_idesc(128, D, p.fmt, 0, 1);
+      const uint64_t qdesc0 = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+      const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sKV), 16, 1024);
+      const uint64_t vdesc0 =
+          smem_desc_sw128(smem_u32(sKV) + NCH * kv_chunk_bytes, kv_chunk_bytes, 1024);
       bool ok = mbar_wait(bar_q, 0, w, FTK_DEV_TIMEOUT_MMA);
       auto issue_s = [&](int i) -> bool {
         const int s = i % NST;
         if (!mbar_wait(bar_kvfull(s), (i / NST) & 1, w, FTK_DEV_TIMEOUT_MMA)) return false;
         tc_fence_after();
-        const uint32_t kbase = smem_u32(sKV) + s * stage_bytes;
+        const uint64_t kdesc = desc_advance(kdesc0, s * stage_bytes);
         const uint32_t d_tmem = tmem + FW_COL_S + (i & 1) * 128;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ks++) {
-          umma_ss(d_tmem,
-                  smem_desc_sw128(smem_u32(sQ) + (ks / 4) * 128 * 128 + (ks % 4) * 32, 16, 1024),
-                  smem_desc_sw128(kbase + (ks / 4) * kv_chunk_bytes + (ks % 4) * 32, 16, 1024),
-                  idesc_s, ks > 0);
+          umma_ss(d_tmem, desc_advance(qdesc0, (ks / 4) * 128 * 128 + (ks % 4) * 32),
+                  desc_advance(kdesc, (ks / 4) * kv_chunk_bytes + (ks % 4) * 32), idesc_s, ks > 0);
         }
         umma_commit(bar_sfull(i & 1));
         return true;
@@ -156,12 +158,11 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int s = i % NST, sb = i & 1;
         if (!mbar_wait(bar_pfull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t vbase = smem_u32(sKV) + s * stage_bytes + NCH * kv_chunk_bytes;
+        const uint64_t vdesc = desc_advance(vdesc0, s * stage_bytes);
         const int ksteps = p.kvb / 16;
         for (int ks = 0; ks < ksteps; ks++) {
           umma_ts(tmem + FW_COL_O + sb * 128, tmem + FW_COL_S + sb * 128 + ks * 8,
-                  smem_desc_sw128(vbase + ks * 2048, kv_chunk_bytes, 1024), idesc_pv,
-                  (i >= 2) || (ks > 0));
+                  desc_advance(vdesc, ks * 2048), idesc_pv, (i >= 2) || (ks > 0));
         }
         umma_commit(bar_kvempty(s));
         // S(i+2) overwrites the columns PV(i) reads P from; the tensor core
