@@ -170,7 +170,8 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     }
   } else if (warp == 1) {
     // -------------------------------------------------------- UMMA issuer
-    if (lane == 0) {
+    {
+      // the whole warp runs this path; one elected lane issues the UMMAs
       const uint32_t idesc = umma_idesc(128, SC_KT, p.fmt, 0, 0);
       const uint64_t qdesc0 = smem_desc_sw128(smem_u32(sQ), 16, 1024);
       const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sK), 16, 1024);
@@ -184,6 +185,7 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
         if (!mbar_wait(bar_kfull(s), ph, w, FTK_DEV_TIMEOUT_MMA)) break;
         tc_fence_after();
         const uint64_t kdesc = desc_advance(kdesc0, s * K_STAGE_BYTES);
+        if (elect_one()) {
 #pragma unroll
         for (int half = 0; half < 2; half++) {
           const uint32_t d_tmem = tmem + static_cast<uint32_t>((a * 2 + half) * SC_KT);
@@ -196,6 +198,8 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
         }
         umma_commit(bar_kempty(s));  // smem stage reusable once these UMMAs retire
         umma_commit(bar_afull(a));   // accumulators readable
+        }
+        __syncwarp();
       }
     }
   } else {

@@ -155,7 +155,8 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n > 0) {
+    if (n > 0) {
+      // the whole warp runs this path; one elected lane issues the UMMAs
       const uint32_t idesc_a = umma_idesc(128, p.kvb, p.fmt, 0, 0);
       const uint32_t idesc_b = umma_idesc(128, D, p.fmt, 0, 1);
       const uint64_t qdesc0 = smem_desc_sw128(smem_u32(sQ), 16, 1024);
@@ -170,6 +171,7 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint64_t kdesc = desc_advance(kdesc0, s * stage_bytes);
         const uint64_t vdesc = desc_advance(kdesc, NCH * kv_chunk_bytes);
         const uint32_t sb = i & 1;
+        if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < D / 16; ks++) {
           const uint32_t qoff = (ks / 4) * 128 * 128 + (ks % 4) * 32;
@@ -185,6 +187,8 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
                   idesc_a, ks > 0);
         }
         umma_commit(bar_afull(sb));
+        }
+        __syncwarp();
         return true;
       };
       if (ok) ok = issue_a(0);
@@ -194,13 +198,17 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
         if (!mbar_wait(bar_dsfull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_MMA)) break;
         tc_fence_after();
         const uint64_t kmn = desc_advance(kmn0, s * stage_bytes);
-        for (int ks = 0; ks < p.kvb / 16; ks++)
-          umma_ts(tmem + 384, tmem + 256 + sb * 32 + ks * 8, desc_advance(kmn, ks * 2048),
-                  idesc_b, (i > 0) || (ks > 0));
-        umma_commit(bar_kvempty(s));
+        if (elect_one()) {
+          for (int ks = 0; ks < p.kvb / 16; ks++)
+            umma_ts(tmem + 384, tmem + 256 + sb * 32 + ks * 8, desc_advance(kmn, ks * 2048),
+                    idesc_b, (i > 0) || (ks > 0));
+          umma_commit(bar_kvempty(s));
+        }
+        __syncwarp();
         if (i + 2 < n) ok = issue_a(i + 2);
       }
-      if (ok) umma_commit(bar_final);
+      if (ok && elect_one()) umma_commit(bar_final);
+      __syncwarp();
     }
   } else {
     // two groups of 128 threads; group w drains the buffers of tiles i = w (mod 2)
@@ -418,7 +426,8 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n > 0) {
+    if (n > 0) {
+      // the whole warp runs this path; one elected lane issues the UMMAs
       const uint32_t idesc_a = umma_idesc(128, p.g, p.fmt, 0, 0);
       const uint32_t idesc_b = umma_idesc(128, D, p.fmt, 0, 1);
       const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sK), 16, 1024);
@@ -433,6 +442,7 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint64_t qdesc = desc_advance(qdesc0, s * stage_bytes);
         const uint64_t dodesc = desc_advance(qdesc, NCH * q_chunk_bytes);
         const uint32_t sb = i & 1;
+        if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < D / 16; ks++) {
           const uint32_t aoff = (ks / 4) * 128 * 128 + (ks % 4) * 32;
@@ -448,6 +458,8 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
                   idesc_a, ks > 0);
         }
         umma_commit(bar_afull(sb));
+        }
+        __syncwarp();
         return true;
       };
       if (ok) ok = issue_a(0);
@@ -458,6 +470,7 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
         tc_fence_after();
         const uint64_t qmn = desc_advance(qmn0, s * stage_bytes);
         const uint64_t domn = desc_advance(qmn, NCH * q_chunk_bytes);
+        if (elect_one()) {
         for (int ks = 0; ks < p.g / 16; ks++) {
           const bool acc = (i > 0) || (ks > 0);
           umma_ts(tmem + 256, tmem + sb * 64 + ks * 8, desc_advance(domn, ks * 2048), idesc_b, acc);
@@ -465,9 +478,12 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
                   acc);
         }
         umma_commit(bar_qempty(s));
+        }
+        __syncwarp();
         if (i + 2 < n) ok = issue_a(i + 2);
       }
-      if (ok) umma_commit(bar_final);
+      if (ok && elect_one()) umma_commit(bar_final);
+      __syncwarp();
     }
   } else {
     // two groups of 128 threads; group w drains the buffers of tiles i = w (mod 2)

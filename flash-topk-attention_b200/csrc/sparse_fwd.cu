@@ -130,7 +130,8 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
   } else if (warp == 1) {
     // -------------------------------------------------------- UMMA issuer
-    if (lane == 0 && n > 0) {
+    if (n > 0) {
+      // the whole warp runs this path; one elected lane issues the UMMAs
       const uint32_t idesc_s = umma_idesc(128, p.kvb, p.fmt, 0, 0);
       const uint32_t idesc_pv = umma_idesc(128, D, p.fmt, 0, 1);
       const uint64_t qdesc0 = smem_desc_sw128(smem_u32(sQ), 16, 1024);
@@ -144,12 +145,16 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tc_fence_after();
         const uint64_t kdesc = desc_advance(kdesc0, s * stage_bytes);
         const uint32_t d_tmem = tmem + FW_COL_S + (i & 1) * 128;
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ks++) {
-          umma_ss(d_tmem, desc_advance(qdesc0, (ks / 4) * 128 * 128 + (ks % 4) * 32),
-                  desc_advance(kdesc, (ks / 4) * kv_chunk_bytes + (ks % 4) * 32), idesc_s, ks > 0);
+          for (int ks = 0; ks < D / 16; ks++) {
+            umma_ss(d_tmem, desc_advance(qdesc0, (ks / 4) * 128 * 128 + (ks % 4) * 32),
+                    desc_advance(kdesc, (ks / 4) * kv_chunk_bytes + (ks % 4) * 32), idesc_s,
+                    ks > 0);
+          }
+          umma_commit(bar_sfull(i & 1));
         }
-        umma_commit(bar_sfull(i & 1));
+        __syncwarp();
         return true;
       };
       if (ok) ok = issue_s(0);
@@ -160,16 +165,20 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tc_fence_after();
         const uint64_t vdesc = desc_advance(vdesc0, s * stage_bytes);
         const int ksteps = p.kvb / 16;
-        for (int ks = 0; ks < ksteps; ks++) {
-          umma_ts(tmem + FW_COL_O + sb * 128, tmem + FW_COL_S + sb * 128 + ks * 8,
-                  desc_advance(vdesc, ks * 2048), idesc_pv, (i >= 2) || (ks > 0));
+        if (elect_one()) {
+          for (int ks = 0; ks < ksteps; ks++) {
+            umma_ts(tmem + FW_COL_O + sb * 128, tmem + FW_COL_S + sb * 128 + ks * 8,
+                    desc_advance(vdesc, ks * 2048), idesc_pv, (i >= 2) || (ks > 0));
+          }
+          umma_commit(bar_kvempty(s));
         }
-        umma_commit(bar_kvempty(s));
+        __syncwarp();
         // S(i+2) overwrites the columns PV(i) reads P from; the tensor core
         // runs UMMAs in issue order, so issuing it after PV(i) is enough.
         if (i + 2 < n) ok = issue_s(i + 2);
       }
-      if (ok) umma_commit(bar_final);
+      if (ok && elect_one()) umma_commit(bar_final);
+      __syncwarp();
     }
   } else {
     // ---------------------------------------------------- softmax threads
