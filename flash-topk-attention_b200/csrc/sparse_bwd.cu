@@ -66,7 +66,10 @@ struct BwdParams {
 };
 
 // ---------------------------------------------------------------------- dQ
-// TMEM columns: S[2] 0/64, dP[2] 128/192, dS[2] 256/288 (packed), dQ 384..
+// TMEM columns: Q 0..63 and dO 64..127 (16-bit pairs: the A operands of the
+// S and dP UMMAs are read from TMEM, which leaves shared-memory bandwidth to
+// the K/V tiles), S[2] 128/192, dP[2] 256/320 (dS written over their first
+// half), dQ 384..
 template <int D>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
@@ -103,6 +106,8 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
   auto bar_dsfull = [&](int s) { return smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 2 + s]); };
   // arrives once, after the last UMMA of the CTA has retired
   const uint32_t bar_final = smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 4]);
+  // Q and dO copied from shared memory into TMEM by the compute warps
+  const uint32_t bar_qt = smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 5]);
 
   if (tid == 0) {
     abort_flag = 0;
@@ -116,6 +121,7 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       mbar_init(bar_dsfull(s), 4);
     }
     mbar_init(bar_final, 1);
+    mbar_init(bar_qt, 8);
     mbar_init_fence();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_do);
@@ -159,11 +165,10 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       // the whole warp runs this path; one elected lane issues the UMMAs
       const uint32_t idesc_a = umma_idesc(128, p.kvb, p.fmt, 0, 0);
       const uint32_t idesc_b = umma_idesc(128, D, p.fmt, 0, 1);
-      const uint64_t qdesc0 = smem_desc_sw128(smem_u32(sQ), 16, 1024);
-      const uint64_t dodesc0 = smem_desc_sw128(smem_u32(sDO), 16, 1024);
       const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sKV), 16, 1024);
       const uint64_t kmn0 = smem_desc_sw128(smem_u32(sKV), kv_chunk_bytes, 1024);
-      bool ok = mbar_wait(bar_q, 0, w, FTK_DEV_TIMEOUT_MMA);
+      bool ok = mbar_wait(bar_qt, 0, w, FTK_DEV_TIMEOUT_MMA);
+      tc_fence_after();
       auto issue_a = [&](int i) -> bool {
         const int s = i % NST;
         if (!mbar_wait(bar_kvfull(s), (i / NST) & 1, w, FTK_DEV_TIMEOUT_MMA)) return false;
@@ -174,17 +179,14 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
         if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < D / 16; ks++) {
-          const uint32_t qoff = (ks / 4) * 128 * 128 + (ks % 4) * 32;
           const uint32_t koff = (ks / 4) * kv_chunk_bytes + (ks % 4) * 32;
-          umma_ss(tmem + sb * 64, desc_advance(qdesc0, qoff), desc_advance(kdesc, koff), idesc_a,
-                  ks > 0);
+          umma_ts(tmem + 128 + sb * 64, tmem + ks * 8, desc_advance(kdesc, koff), idesc_a, ks > 0);
         }
 #pragma unroll
         for (int ks = 0; ks < D / 16; ks++) {
-          const uint32_t qoff = (ks / 4) * 128 * 128 + (ks % 4) * 32;
           const uint32_t koff = (ks / 4) * kv_chunk_bytes + (ks % 4) * 32;
-          umma_ss(tmem + 128 + sb * 64, desc_advance(dodesc0, qoff), desc_advance(vdesc, koff),
-                  idesc_a, ks > 0);
+          umma_ts(tmem + 256 + sb * 64, tmem + 64 + ks * 8, desc_advance(vdesc, koff), idesc_a,
+                  ks > 0);
         }
         umma_commit(bar_afull(sb));
         }
@@ -200,7 +202,7 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint64_t kmn = desc_advance(kmn0, s * stage_bytes);
         if (elect_one()) {
           for (int ks = 0; ks < p.kvb / 16; ks++)
-            umma_ts(tmem + 384, tmem + 256 + sb * 32 + ks * 8, desc_advance(kmn, ks * 2048),
+            umma_ts(tmem + 384, tmem + 256 + sb * 64 + ks * 8, desc_advance(kmn, ks * 2048),
                     idesc_b, (i > 0) || (ks > 0));
           umma_commit(bar_kvempty(s));
         }
@@ -219,9 +221,9 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
     const int qrow = tile_row0 + r;
     const bool row_valid = (grp < groups) && qrow >= 0 && qrow < p.N;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t s_addr = lane_addr + wg * 64;
-    const uint32_t dp_addr = lane_addr + 128 + wg * 64;
-    const uint32_t ds_addr = lane_addr + 256 + wg * 32;
+    const uint32_t s_addr = lane_addr + 128 + wg * 64;
+    const uint32_t dp_addr = lane_addr + 256 + wg * 64;
+    const uint32_t ds_addr = dp_addr;   // dS chunk k lands on dP columns already read
     const float c = p.scale_log2;
     float lse2 = 0.f, dl = 0.f;
     if (row_valid) {
@@ -229,6 +231,32 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       dl = p.delta[static_cast<int64_t>(bh) * p.N + qrow];
     }
     bool ok = true;
+    if (n > 0) {
+      // group 0 moves the Q tile, group 1 the dO tile, from (swizzled) shared
+      // memory into TMEM: row r -> lane r, two 16-bit values per column
+      ok = mbar_wait(bar_q, 0, w, FTK_DEV_TIMEOUT_CONSUMER);
+      if (ok) {
+        const uint8_t* src = wg == 0 ? sQ : sDO;
+#pragma unroll
+        for (int ch = 0; ch < NCH; ch++) {
+          uint32_t v[32];
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const uint4 t4 = *reinterpret_cast<const uint4*>(src + ch * 128 * 128 +
+                                                             sw128_offset(r, j));
+            v[j * 4 + 0] = t4.x;
+            v[j * 4 + 1] = t4.y;
+            v[j * 4 + 2] = t4.z;
+            v[j * 4 + 3] = t4.w;
+          }
+          tmem_st32(lane_addr + wg * 64 + ch * 32, v);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_qt);
+    }
     for (int i = wg; ok && i < n; i += 2) {
       // A(i) complete also means B(i-2) has retired (same issue order), so the
       // dS columns of this buffer are free again.
