@@ -30,8 +30,12 @@ namespace ftk {
 
 constexpr int FW_THREADS = 320;  // 2 + 2 x 4 warps
 constexpr int FW_MAX_STAGES = 4;
-constexpr int FW_COL_S = 0;      // S[2] (P written over them): 2 x 128 columns
-constexpr int FW_COL_O = 256;    // O[2]: 2 x 128 columns
+// TMEM columns.  kv blocks of at most 64 rows: Q (16-bit pairs) 0..63, S[2]
+// at 64 / 128, so the S UMMAs read their A operand from TMEM and shared-memory
+// bandwidth is left to the K/V tiles (an SS UMMA of this shape spends more
+// time fetching Q than multiplying).  Larger kv blocks: S[2] at 0 / 128 and Q
+// stays in shared memory.  P is written over the S columns.  O[2] at 256 / 384.
+constexpr int FW_COL_O = 256;
 
 struct FwdParams {
   int N, H, QM, W, Mkv;
@@ -57,7 +61,7 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint8_t* sQ = smem;
   uint8_t* sKV = smem + Q_BYTES;
   __shared__ UnionScratch un;
-  __shared__ __align__(8) uint64_t bars[2 + 2 * FW_MAX_STAGES + 4];
+  __shared__ __align__(8) uint64_t bars[3 + 2 * FW_MAX_STAGES + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
   __shared__ float s_m[2][128], s_l[2][128];
@@ -74,15 +78,19 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
   const uint32_t bar_q = smem_u32(&bars[0]);
   const uint32_t bar_final = smem_u32(&bars[1]);
-  auto bar_kvfull = [&](int s) { return smem_u32(&bars[2 + s]); };
-  auto bar_kvempty = [&](int s) { return smem_u32(&bars[2 + FW_MAX_STAGES + s]); };
-  auto bar_sfull = [&](int s) { return smem_u32(&bars[2 + 2 * FW_MAX_STAGES + s]); };
-  auto bar_pfull = [&](int s) { return smem_u32(&bars[2 + 2 * FW_MAX_STAGES + 2 + s]); };
+  const uint32_t bar_qt = smem_u32(&bars[2]);   // Q copied into TMEM
+  auto bar_kvfull = [&](int s) { return smem_u32(&bars[3 + s]); };
+  auto bar_kvempty = [&](int s) { return smem_u32(&bars[3 + FW_MAX_STAGES + s]); };
+  auto bar_sfull = [&](int s) { return smem_u32(&bars[3 + 2 * FW_MAX_STAGES + s]); };
+  auto bar_pfull = [&](int s) { return smem_u32(&bars[3 + 2 * FW_MAX_STAGES + 2 + s]); };
+  const bool q_tmem = p.kvb <= 64;
+  const uint32_t s_col0 = q_tmem ? 64u : 0u, s_stride = q_tmem ? 64u : 128u;
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(bar_q, 1);
     mbar_init(bar_final, 1);
+    mbar_init(bar_qt, 4);
     for (int s = 0; s < FW_MAX_STAGES; s++) {
       mbar_init(bar_kvfull(s), 1);
       mbar_init(bar_kvempty(s), 1);
@@ -138,19 +146,27 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sKV), 16, 1024);
       const uint64_t vdesc0 =
           smem_desc_sw128(smem_u32(sKV) + NCH * kv_chunk_bytes, kv_chunk_bytes, 1024);
-      bool ok = mbar_wait(bar_q, 0, w, FTK_DEV_TIMEOUT_MMA);
+      bool ok = mbar_wait(q_tmem ? bar_qt : bar_q, 0, w, FTK_DEV_TIMEOUT_MMA);
+      tc_fence_after();
       auto issue_s = [&](int i) -> bool {
         const int s = i % NST;
         if (!mbar_wait(bar_kvfull(s), (i / NST) & 1, w, FTK_DEV_TIMEOUT_MMA)) return false;
         tc_fence_after();
         const uint64_t kdesc = desc_advance(kdesc0, s * stage_bytes);
-        const uint32_t d_tmem = tmem + FW_COL_S + (i & 1) * 128;
+        const uint32_t d_tmem = tmem + s_col0 + (i & 1) * s_stride;
         if (elect_one()) {
+          if (q_tmem) {
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ks++) {
-            umma_ss(d_tmem, desc_advance(qdesc0, (ks / 4) * 128 * 128 + (ks % 4) * 32),
-                    desc_advance(kdesc, (ks / 4) * kv_chunk_bytes + (ks % 4) * 32), idesc_s,
-                    ks > 0);
+            for (int ks = 0; ks < D / 16; ks++)
+              umma_ts(d_tmem, tmem + ks * 8,
+                      desc_advance(kdesc, (ks / 4) * kv_chunk_bytes + (ks % 4) * 32), idesc_s,
+                      ks > 0);
+          } else {
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ks++)
+              umma_ss(d_tmem, desc_advance(qdesc0, (ks / 4) * 128 * 128 + (ks % 4) * 32),
+                      desc_advance(kdesc, (ks / 4) * kv_chunk_bytes + (ks % 4) * 32), idesc_s,
+                      ks > 0);
           }
           umma_commit(bar_sfull(i & 1));
         }
@@ -167,7 +183,7 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int ksteps = p.kvb / 16;
         if (elect_one()) {
           for (int ks = 0; ks < ksteps; ks++) {
-            umma_ts(tmem + FW_COL_O + sb * 128, tmem + FW_COL_S + sb * 128 + ks * 8,
+            umma_ts(tmem + FW_COL_O + sb * 128, tmem + s_col0 + sb * s_stride + ks * 8,
                     desc_advance(vdesc, ks * 2048), idesc_pv, (i >= 2) || (ks > 0));
           }
           umma_commit(bar_kvempty(s));
@@ -189,11 +205,37 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int qrow = tile_row0 + r;
     const bool row_valid = (grp < groups) && qrow >= 0 && qrow < p.N;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t s_addr = lane_addr + FW_COL_S + grp_w * 128;
+    const uint32_t s_addr = lane_addr + s_col0 + grp_w * s_stride;
     const uint32_t o_addr = lane_addr + FW_COL_O + grp_w * 128;
     const float c = p.scale_log2;
     float m_run = -INFINITY, l = 0.f;
     bool ok = true;
+
+    if (q_tmem && n > 0 && grp_w == 0) {
+      // group 0 moves the Q tile from (swizzled) shared memory into TMEM:
+      // row r -> lane r, two 16-bit values per column
+      ok = mbar_wait(bar_q, 0, w, FTK_DEV_TIMEOUT_CONSUMER);
+      if (ok) {
+#pragma unroll
+        for (int ch = 0; ch < NCH; ch++) {
+          uint32_t v[32];
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const uint4 t4 =
+                *reinterpret_cast<const uint4*>(sQ + ch * 128 * 128 + sw128_offset(r, j));
+            v[j * 4 + 0] = t4.x;
+            v[j * 4 + 1] = t4.y;
+            v[j * 4 + 2] = t4.z;
+            v[j * 4 + 3] = t4.w;
+          }
+          tmem_st32(lane_addr + ch * 32, v);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_qt);
+    }
 
     for (int i = grp_w; ok && i < n; i += 2) {
       // S(i) complete also means PV(i-2) has retired (same issue order), so
