@@ -47,7 +47,7 @@ __global__ void delta_kernel(const uint8_t* __restrict__ o, const uint8_t* __res
   if (lane == 0) delta[(b * H + h) * N + n] = acc;
 }
 
-constexpr int BW_THREADS = 320;  // 2 + 2 x 4 warps
+constexpr int BW_THREADS = 576;  // 2 + 2 x 8 warps
 constexpr int BW_MAX_STAGES = 4;
 
 struct BwdParams {
@@ -118,10 +118,10 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
     for (int s = 0; s < 2; s++) {
       mbar_init(bar_afull(s), 1);
-      mbar_init(bar_dsfull(s), 4);
+      mbar_init(bar_dsfull(s), 8);  // one arrival per warp of the owning group
     }
     mbar_init(bar_final, 1);
-    mbar_init(bar_qt, 8);
+    mbar_init(bar_qt, 8);   // the 8 warps that copy Q / dO
     mbar_init_fence();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_do);
@@ -139,6 +139,7 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
   WaitCtx w{&abort_flag, p.status};
+  const bool split = (p.kvb % 32) == 0;   // kv columns of a tile shared by two warps per row
 
   if (warp == 0) {
     if (lane == 0 && n > 0) {
@@ -167,6 +168,10 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       const uint32_t idesc_b = umma_idesc(128, D, p.fmt, 0, 1);
       const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sKV), 16, 1024);
       const uint64_t kmn0 = smem_desc_sw128(smem_u32(sKV), kv_chunk_bytes, 1024);
+      // dS column of k-step ks: each half of the kv columns is written by its
+      // own warps over the dP columns those warps read (see the compute part)
+      const int kh = split ? p.kvb / 32 : p.kvb / 16;
+      auto ds_col = [&](int ks) { return (ks / kh) * (p.kvb / 2) + (ks % kh) * 8; };
       bool ok = mbar_wait(bar_qt, 0, w, FTK_DEV_TIMEOUT_MMA);
       tc_fence_after();
       auto issue_a = [&](int i) -> bool {
@@ -202,7 +207,7 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint64_t kmn = desc_advance(kmn0, s * stage_bytes);
         if (elect_one()) {
           for (int ks = 0; ks < p.kvb / 16; ks++)
-            umma_ts(tmem + 384, tmem + 256 + sb * 64 + ks * 8, desc_advance(kmn, ks * 2048),
+            umma_ts(tmem + 384, tmem + 256 + sb * 64 + ds_col(ks), desc_advance(kmn, ks * 2048),
                     idesc_b, (i > 0) || (ks > 0));
           umma_commit(bar_kvempty(s));
         }
@@ -213,8 +218,13 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       __syncwarp();
     }
   } else {
-    // two groups of 128 threads; group w drains the buffers of tiles i = w (mod 2)
-    const int wg = (warp - 2) >> 2;
+    // Two groups of 8 warps; group w drains the buffers of tiles i = w (mod 2).
+    // Inside a group two warps share each 32-row lane quarter and take one
+    // half of the kv columns each, so a tile's latency-bound per-thread work
+    // is 32 columns long and 4 compute warps per scheduler hide each other.
+    const int cw = warp - 2;
+    const int wg = cw >> 3;
+    const int colhalf = (cw >> 2) & 1;
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const int grp = r / p.g;
@@ -223,7 +233,8 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
     const uint32_t s_addr = lane_addr + 128 + wg * 64;
     const uint32_t dp_addr = lane_addr + 256 + wg * 64;
-    const uint32_t ds_addr = dp_addr;   // dS chunk k lands on dP columns already read
+    const int cbeg = split ? colhalf * (p.kvb / 2) : 0;
+    const int cend = split ? cbeg + p.kvb / 2 : (colhalf == 0 ? p.kvb : 0);
     const float c = p.scale_log2;
     float lse2 = 0.f, dl = 0.f;
     if (row_valid) {
@@ -231,7 +242,7 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       dl = p.delta[static_cast<int64_t>(bh) * p.N + qrow];
     }
     bool ok = true;
-    if (n > 0) {
+    if (n > 0 && colhalf == 0) {
       // group 0 moves the Q tile, group 1 the dO tile, from (swizzled) shared
       // memory into TMEM: row r -> lane r, two 16-bit values per column
       ok = mbar_wait(bar_q, 0, w, FTK_DEV_TIMEOUT_CONSUMER);
@@ -269,8 +280,11 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       const int lo = max(0, -tok0), hi = min(p.kvb, p.N - tok0);
       const bool act = row_valid && ((un.masks[i] >> grp) & 1) && hi > lo;
       const bool fast = __all_sync(0xffffffffu, act) && lo == 0 && hi == p.kvb;
-      for (int c0 = 0; c0 < p.kvb; c0 += 32) {
-        if (p.kvb - c0 >= 32) {
+      // dS of columns [c0, c0+w) is written over dP columns [cbeg + (c0-cbeg)/2, ..):
+      // columns this thread has already read, never another warp's
+      for (int c0 = cbeg; c0 < cend; c0 += 32) {
+        const uint32_t ds_addr = dp_addr + cbeg + ((c0 - cbeg) >> 1);
+        if (cend - c0 >= 32) {
           uint32_t sv[32], dv[32], pk[16];
           tmem_ld32(s_addr + c0, sv);
           tmem_ld32(dp_addr + c0, dv);
@@ -296,7 +310,7 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
               pk[x >> 1] = pack2(d0, d1, p.fmt);
             }
           }
-          tmem_st16(ds_addr + (c0 >> 1), pk);
+          tmem_st16(ds_addr, pk);
         } else {
           uint32_t sv[16], dv[16], pk[8];
           tmem_ld16(s_addr + c0, sv);
@@ -313,7 +327,7 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
                    (__uint_as_float(dv[x + 1]) - dl);
             pk[x >> 1] = pack2(d0, d1, p.fmt);
           }
-          tmem_st8(ds_addr + (c0 >> 1), pk);
+          tmem_st8(ds_addr, pk);
         }
       }
       tmem_wait_st();
@@ -331,8 +345,9 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
         orow = static_cast<uint8_t*>(p.out0) +
                2 * (static_cast<int64_t>(b_idx) * p.s0_b + static_cast<int64_t>(qrow) * p.s0_n +
                     static_cast<int64_t>(h_idx) * p.s0_h);
-      constexpr int HALF = D / 2;
-      for (int c0 = wg * HALF; c0 < (wg + 1) * HALF; c0 += 32) {
+      // 32-column chunks of the head dim are dealt round-robin to the four
+      // warps of a lane quarter
+      for (int c0 = (wg * 2 + colhalf) * 32; c0 < D; c0 += 128) {
         uint32_t v[32];
         if (n > 0) {
           tmem_ld32(lane_addr + 384 + c0, v);
@@ -382,7 +397,7 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
   __shared__ __align__(8) uint64_t bars[1 + 2 * BW_MAX_STAGES + 6];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
-  __shared__ __align__(16) float s_lse2[2][2][128], s_delta[2][2][128];
+  __shared__ __align__(16) float s_lse2[2][2][128], s_delta[2][2][128];  // [group][parity][q row]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int j0 = blockIdx.x * p.G;          // first kv block of the tile
@@ -411,7 +426,7 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
     for (int s = 0; s < 2; s++) {
       mbar_init(bar_afull(s), 1);
-      mbar_init(bar_pfull(s), 4);
+      mbar_init(bar_pfull(s), 8);  // one arrival per warp of the owning group
     }
     mbar_init(bar_final, 1);
     mbar_init_fence();
@@ -432,6 +447,7 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
   WaitCtx w{&abort_flag, p.status};
+  const bool split = (p.g % 32) == 0;   // q columns of a tile shared by two warps per row
 
   if (warp == 0) {
     if (lane == 0 && n > 0) {
@@ -462,6 +478,10 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
       const uint64_t vdesc0 = smem_desc_sw128(smem_u32(sV), 16, 1024);
       const uint64_t qdesc0 = smem_desc_sw128(smem_u32(sQD), 16, 1024);
       const uint64_t qmn0 = smem_desc_sw128(smem_u32(sQD), q_chunk_bytes, 1024);
+      // P^T / dS^T column of k-step ks: each half of the q columns is written
+      // by its own warps over the columns those warps read
+      const int kh = split ? p.g / 32 : p.g / 16;
+      auto pt_col = [&](int ks) { return (ks / kh) * (p.g / 2) + (ks % kh) * 8; };
       bool ok = mbar_wait(bar_kv, 0, w, FTK_DEV_TIMEOUT_MMA);
       auto issue_a = [&](int i) -> bool {
         const int s = i % NST;
@@ -501,9 +521,10 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
         if (elect_one()) {
         for (int ks = 0; ks < p.g / 16; ks++) {
           const bool acc = (i > 0) || (ks > 0);
-          umma_ts(tmem + 256, tmem + sb * 64 + ks * 8, desc_advance(domn, ks * 2048), idesc_b, acc);
-          umma_ts(tmem + 384, tmem + 128 + sb * 64 + ks * 8, desc_advance(qmn, ks * 2048), idesc_b,
+          umma_ts(tmem + 256, tmem + sb * 64 + pt_col(ks), desc_advance(domn, ks * 2048), idesc_b,
                   acc);
+          umma_ts(tmem + 384, tmem + 128 + sb * 64 + pt_col(ks), desc_advance(qmn, ks * 2048),
+                  idesc_b, acc);
         }
         umma_commit(bar_qempty(s));
         }
@@ -514,21 +535,27 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
       __syncwarp();
     }
   } else {
-    // two groups of 128 threads; group w drains the buffers of tiles i = w (mod 2)
-    const int wg = (warp - 2) >> 2;
+    // Two groups of 8 warps; group w drains the buffers of tiles i = w (mod 2).
+    // Inside a group two warps share each 32-row lane quarter and take one
+    // half of the q columns each.
+    const int cw = warp - 2;
+    const int wg = cw >> 3;
+    const int colhalf = (cw >> 2) & 1;
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
-    const int ct = (tid - 64) & 127;         // index inside the group
+    const int ct = (tid - 64) & 255;         // index inside the group
     const int grp = r / p.kvb;
     const int tok = tile_tok0 + r;
     const bool row_valid = (grp < groups) && tok >= 0 && tok < p.N;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
     const uint32_t st_addr = lane_addr + wg * 64;         // S^T, then P^T
     const uint32_t dp_addr = lane_addr + 128 + wg * 64;   // dP^T, then dS^T
+    const int cbeg = split ? colhalf * (p.g / 2) : 0;
+    const int cend = split ? cbeg + p.g / 2 : (colhalf == 0 ? p.g : 0);
     const float c = p.scale_log2;
     bool ok = true;
     // every thread of a group runs all of the group's rounds (its named
-    // barrier needs all 128); after a failed wait a thread only keeps the
+    // barrier needs all 256); after a failed wait a thread only keeps the
     // barrier company and does no more work.
     for (int i = wg; i < n; i += 2) {
       const int pb = (i >> 1) & 1;           // per-group double buffer of lse / delta
@@ -544,9 +571,9 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
         s_delta[wg][pb][ct] = dl;
       }
       if (wg == 0)
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
       else
-        asm volatile("bar.sync 2, 128;" ::: "memory");
+        asm volatile("bar.sync 2, 256;" ::: "memory");
       if (!ok) continue;
       if (!mbar_wait(bar_afull(wg), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) {
         ok = false;
@@ -558,32 +585,53 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
       const bool fast = __all_sync(0xffffffffu, act) && lo == 0 && hi == p.g;
       const float4* l4 = reinterpret_cast<const float4*>(s_lse2[wg][pb]);
       const float4* d4 = reinterpret_cast<const float4*>(s_delta[wg][pb]);
-      for (int c0 = 0; c0 < p.g; c0 += 16) {
+      // P^T / dS^T of columns [c0, c0+16) go over columns cbeg + (c0-cbeg)/2 ..
+      // of the S^T / dP^T regions: columns this thread has already read
+      for (int c0 = cbeg; c0 < cend; c0 += 16) {
         uint32_t sv[16], dv[16], pp[8], pd[8];
         tmem_ld16(st_addr + c0, sv);
         tmem_ld16(dp_addr + c0, dv);
         tmem_wait_ld();
+        if (fast) {
 #pragma unroll
-        for (int x = 0; x < 16; x += 4) {
-          const float4 lq = l4[(c0 + x) >> 2];
-          const float4 dq = d4[(c0 + x) >> 2];
-          const float ls[4] = {lq.x, lq.y, lq.z, lq.w};
-          const float ds[4] = {dq.x, dq.y, dq.z, dq.w};
-          float pv[4], dsv[4];
-#pragma unroll
-          for (int y = 0; y < 4; y++) {
-            const bool on = fast || (act && c0 + x + y >= lo && c0 + x + y < hi);
-            const float pr = on ? fast_exp2(fmaf(__uint_as_float(sv[x + y]), c, -ls[y])) : 0.f;
-            pv[y] = pr;
-            dsv[y] = pr * (__uint_as_float(dv[x + y]) - ds[y]);
+          for (int x = 0; x < 16; x += 4) {
+            const float4 lq = l4[(c0 + x) >> 2];
+            const float4 dq = d4[(c0 + x) >> 2];
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[x + 0]), c, -lq.x));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[x + 1]), c, -lq.y));
+            const float p2 = fast_exp2(fmaf(__uint_as_float(sv[x + 2]), c, -lq.z));
+            const float p3 = fast_exp2(fmaf(__uint_as_float(sv[x + 3]), c, -lq.w));
+            pp[x >> 1] = pack2(p0, p1, p.fmt);
+            pp[(x >> 1) + 1] = pack2(p2, p3, p.fmt);
+            pd[x >> 1] = pack2(p0 * (__uint_as_float(dv[x + 0]) - dq.x),
+                               p1 * (__uint_as_float(dv[x + 1]) - dq.y), p.fmt);
+            pd[(x >> 1) + 1] = pack2(p2 * (__uint_as_float(dv[x + 2]) - dq.z),
+                                     p3 * (__uint_as_float(dv[x + 3]) - dq.w), p.fmt);
           }
-          pp[x >> 1] = pack2(pv[0], pv[1], p.fmt);
-          pp[(x >> 1) + 1] = pack2(pv[2], pv[3], p.fmt);
-          pd[x >> 1] = pack2(dsv[0], dsv[1], p.fmt);
-          pd[(x >> 1) + 1] = pack2(dsv[2], dsv[3], p.fmt);
+        } else {
+#pragma unroll
+          for (int x = 0; x < 16; x += 4) {
+            const float4 lq = l4[(c0 + x) >> 2];
+            const float4 dq = d4[(c0 + x) >> 2];
+            const float ls[4] = {lq.x, lq.y, lq.z, lq.w};
+            const float ds[4] = {dq.x, dq.y, dq.z, dq.w};
+            float pv[4], dsv[4];
+#pragma unroll
+            for (int y = 0; y < 4; y++) {
+              const bool on = act && c0 + x + y >= lo && c0 + x + y < hi;
+              const float pr = on ? fast_exp2(fmaf(__uint_as_float(sv[x + y]), c, -ls[y])) : 0.f;
+              pv[y] = pr;
+              dsv[y] = pr * (__uint_as_float(dv[x + y]) - ds[y]);
+            }
+            pp[x >> 1] = pack2(pv[0], pv[1], p.fmt);
+            pp[(x >> 1) + 1] = pack2(pv[2], pv[3], p.fmt);
+            pd[x >> 1] = pack2(dsv[0], dsv[1], p.fmt);
+            pd[(x >> 1) + 1] = pack2(dsv[2], dsv[3], p.fmt);
+          }
         }
-        tmem_st8(st_addr + (c0 >> 1), pp);
-        tmem_st8(dp_addr + (c0 >> 1), pd);
+        const int oc = cbeg + ((c0 - cbeg) >> 1);
+        tmem_st8(st_addr + oc, pp);
+        tmem_st8(dp_addr + oc, pd);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -604,7 +652,7 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
       if (row_valid)
         orow = base + 2 * (static_cast<int64_t>(b_idx) * sb_ + static_cast<int64_t>(tok) * sn_ +
                            static_cast<int64_t>(h_idx) * sh_);
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      for (int c0 = colhalf * 32; c0 < D; c0 += 64) {
         uint32_t v[32];
         if (n > 0) {
           tmem_ld32(lane_addr + 256 + which * 128 + c0, v);
