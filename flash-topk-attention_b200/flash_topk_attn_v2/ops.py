@@ -34,6 +34,43 @@ def _count(n: int) -> None:
     _launches += n
 
 
+# Optional per-call CUDA-event timing (off by default; bench.py switches it on
+# around its timed loop).  Every C-ABI call is bracketed by two events on the
+# stream it launches on; `event_times()` returns milliseconds per entry point.
+_events = None
+
+
+def enable_event_timing(on: bool) -> None:
+    global _events
+    _events = [] if on else None
+
+
+def _call(name, fn, *args) -> None:
+    """Run one C-ABI entry point, map its return code, time it when asked."""
+    if _events is None:
+        check(fn(*args), name)
+        return
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    rc = fn(*args)
+    e1.record()
+    _events.append((name, e0, e1))
+    check(rc, name)
+
+
+def event_times() -> dict:
+    """Sum of device milliseconds and call count per entry point since
+    enable_event_timing(True); synchronises."""
+    out = {}
+    if _events:
+        torch.cuda.synchronize()
+        for name, e0, e1 in _events:
+            ms, n = out.get(name, (0.0, 0))
+            out[name] = (ms + e0.elapsed_time(e1), n + 1)
+    return out
+
+
 def status_word(device) -> torch.Tensor:
     """Sticky per-device status word handed to every launch."""
     dev = torch.device(device)
@@ -188,10 +225,10 @@ def flash_block_score(q, k, num_heads, score_block_size, padding=(0, 0)):
     flat = out.view(B * H, N, M)
     for b0 in range(0, B * H, step):
         cnt = min(step, B * H - b0)
-        check(lib.ftk_block_score(
+        _call("ftk_block_score", lib.ftk_block_score, 
             ptr(qq), ptr(kk), _lib.dtype_code(qq), B, H, N, Dk, *sq, *sk, b0, cnt,
             score_block_size, ph, pt, float(D) ** -0.5, ptr(flat[b0]), ptr(ws), ws.numel(),
-            ptr(status), stream_ptr(q.device)), "ftk_block_score")
+            ptr(status), stream_ptr(q.device))
         _count(4)
     _after(q.device)
     return out
@@ -235,10 +272,9 @@ def flash_topk_select(block_scores, threshold, max_topk, score_block_size, paddi
     idx = torch.empty(B, H, N, m_out, dtype=torch.int32, device=dev)
     raw = torch.empty(B, H, N, m_out, dtype=torch.float32, device=dev)
     avg = torch.empty(B, H, N, m_out, dtype=torch.float32, device=dev)
-    check(lib.ftk_topk_select(
+    _call("ftk_topk_select", lib.ftk_topk_select, 
         ptr(scores), 0, B * H * N, M, max_topk, score_block_size, pad_head, pad_tail,
-        float(threshold), ptr(idx), ptr(raw), ptr(avg), ptr(status_word(dev)), stream_ptr(dev)),
-        "ftk_topk_select")
+        float(threshold), ptr(idx), ptr(raw), ptr(avg), ptr(status_word(dev)), stream_ptr(dev))
     _count(1)
     _after(dev)
     return idx, raw, avg
@@ -265,11 +301,11 @@ def flash_topk_score_fused(q, k, num_heads, score_block_size, topk, padding, thr
     fi, fr, fa = (t.view(B * H, N, m_out) for t in (idx, raw, avg))
     for b0 in range(0, B * H, step):
         cnt = min(step, B * H - b0)
-        check(lib.ftk_score_topk(
+        _call("ftk_score_topk", lib.ftk_score_topk, 
             ptr(qq), ptr(kk), _lib.dtype_code(qq), B, H, N, Dk, *sq, *sk, b0, cnt,
             score_block_size, ph, pt, float(D) ** -0.5, topk, float(threshold),
             ptr(fi[b0]), ptr(fr[b0]), ptr(fa[b0]), ptr(ws), ws.numel(), ptr(status),
-            stream_ptr(dev)), "ftk_score_topk")
+            stream_ptr(dev))
         _count(4)
     _after(dev)
     # lets build_qblock_topk_indices size its table without a device round trip
@@ -311,10 +347,9 @@ def flash_qblock_merge(topk_indices, topk_scores, q_block_size, qblock_topk, num
     merged = torch.empty(B, H, QM, qblock_topk, dtype=torch.int32, device=dev)
     mscores = torch.empty(B, H, QM, qblock_topk, dtype=torch.float32, device=dev)
     counts = torch.empty(B, H, QM, dtype=torch.int32, device=dev)
-    check(lib.ftk_qblock_merge(
+    _call("ftk_qblock_merge", lib.ftk_qblock_merge, 
         ptr(idx), ptr(scr), B * H, N, K, q_block_size, qh, qt, num_score_blocks, qblock_topk,
-        ptr(merged), ptr(mscores), ptr(counts), ptr(status_word(dev)), stream_ptr(dev)),
-        "ftk_qblock_merge")
+        ptr(merged), ptr(mscores), ptr(counts), ptr(status_word(dev)), stream_ptr(dev))
     _count(1)
     _after(dev)
     if return_counts:
@@ -339,9 +374,9 @@ def flash_build_reverse_indices_cuda(merged_indices, counts, num_kv_blocks):
     rc = torch.empty(B, H, M, dtype=torch.int32, device=dev)
     skv = torch.empty(B, H, M, dtype=torch.int32, device=dev)
     ws = torch.empty(lib.ftk_build_reverse_workspace(B * H, QM, M), dtype=torch.uint8, device=dev)
-    check(lib.ftk_build_reverse(
+    _call("ftk_build_reverse", lib.ftk_build_reverse, 
         ptr(merged), ptr(cnt), B * H, QM, W, M, ptr(rev), ptr(rc), ptr(skv), ptr(ws), ws.numel(),
-        ptr(status_word(dev)), stream_ptr(dev)), "ftk_build_reverse")
+        ptr(status_word(dev)), stream_ptr(dev))
     _count(3)
     _after(dev)
     return rev, rc, skv
@@ -359,8 +394,8 @@ def flash_sort_by_count_cuda(reverse_counts, num_heads, num_kv_blocks):
     sc = torch.empty_like(flat)
     ids = torch.empty(total, dtype=torch.int32, device=dev)
     ws = torch.empty(lib.ftk_sort_by_count_workspace(total, max_val), dtype=torch.uint8, device=dev)
-    check(lib.ftk_sort_by_count(ptr(flat), total, max_val, ptr(sc), ptr(ids), ptr(ws), ws.numel(),
-                                stream_ptr(dev)), "ftk_sort_by_count")
+    _call("ftk_sort_by_count", lib.ftk_sort_by_count, ptr(flat), total, max_val, ptr(sc), ptr(ids), ptr(ws), ws.numel(),
+                                stream_ptr(dev))
     _count(3)
     return sc, ids
 
@@ -395,12 +430,12 @@ class FlashSparseAttnFunc(torch.autograd.Function):
         QM, W = merged.shape[2], merged.shape[3]
         o = torch.empty(B, N, C, dtype=q.dtype, device=dev)
         lse = torch.empty(B, H, N, dtype=torch.float32, device=dev)
-        check(lib.ftk_sparse_fwd(
+        _call("ftk_sparse_fwd", lib.ftk_sparse_fwd, 
             ptr(qq), ptr(kk), ptr(vv), _lib.dtype_code(qq), B, H, N, D,
             sq_b, sq_n, sq_h, sk_b, sk_n, sk_h, sv_b, sv_n, sv_h,
             ptr(merged), QM, W, q_block_size, kv_block_size, q_pad_head, kv_pad_head,
             float(scale), ptr(o), N * C, C, D, ptr(lse), ptr(status_word(dev)),
-            stream_ptr(dev)), "ftk_sparse_fwd")
+            stream_ptr(dev))
         _count(1)
         _after(dev)
         ctx.save_for_backward(qq, kk, vv, o, lse, merged)
@@ -427,19 +462,18 @@ class FlashSparseAttnFunc(torch.autograd.Function):
         dk = torch.empty(B, N, C, dtype=qq.dtype, device=dev)
         dv = torch.empty(B, N, C, dtype=qq.dtype, device=dev)
         dt = _lib.dtype_code(qq)
-        check(lib.ftk_sparse_bwd_dq(
+        _call("ftk_sparse_bwd_dq", lib.ftk_sparse_bwd_dq, 
             ptr(qq), ptr(kk), ptr(vv), ptr(o), ptr(do), dt, B, H, N, D,
             sq_b, sq_n, sq_h, sk_b, sk_n, sk_h, sv_b, sv_n, sv_h, N * C, C, D,
             sdo_b, sdo_n, sdo_h, ptr(merged), QM, W, g, kvb, qph, kph, scale,
-            ptr(lse), ptr(delta), ptr(dq), N * C, C, D, ptr(status), st), "ftk_sparse_bwd_dq")
+            ptr(lse), ptr(delta), ptr(dq), N * C, C, D, ptr(status), st)
         _count(2)
         rev, rc, skv = flash_build_reverse_indices_cuda(merged, None, M)
-        check(lib.ftk_sparse_bwd_dkv(
+        _call("ftk_sparse_bwd_dkv", lib.ftk_sparse_bwd_dkv, 
             ptr(qq), ptr(kk), ptr(vv), ptr(do), dt, B, H, N, D,
             sq_b, sq_n, sq_h, sk_b, sk_n, sk_h, sv_b, sv_n, sv_h, sdo_b, sdo_n, sdo_h,
             ptr(rev), ptr(rc), ptr(skv), QM, M, g, kvb, qph, kph, scale,
-            ptr(lse), ptr(delta), ptr(dk), N * C, C, D, ptr(dv), N * C, C, D, ptr(status), st),
-            "ftk_sparse_bwd_dkv")
+            ptr(lse), ptr(delta), ptr(dk), N * C, C, D, ptr(dv), N * C, C, D, ptr(status), st)
         _count(1)
         _after(dev)
         return dq, dk, dv, None, None, None, None, None, None, None, None
