@@ -100,7 +100,7 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = smem + Q_BYTES;
-  __shared__ __align__(8) uint64_t bars[1 + 2 * SC_STAGES + 4 + 2];
+  __shared__ __align__(8) uint64_t bars[1 + 2 * SC_STAGES + 8 + 2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
   __shared__ float s_mref[SC_QROWS];   // group 0 -> group 1: reference exponent
@@ -115,10 +115,15 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
   const uint32_t bar_q = smem_u32(&bars[0]);
   auto bar_kfull = [&](int s) { return smem_u32(&bars[1 + s]); };
   auto bar_kempty = [&](int s) { return smem_u32(&bars[1 + SC_STAGES + s]); };
-  auto bar_afull = [&](int s) { return smem_u32(&bars[1 + 2 * SC_STAGES + s]); };
-  auto bar_aempty = [&](int s) { return smem_u32(&bars[1 + 2 * SC_STAGES + 2 + s]); };
-  const uint32_t bar_mref = smem_u32(&bars[1 + 2 * SC_STAGES + 4]);
-  const uint32_t bar_part = smem_u32(&bars[1 + 2 * SC_STAGES + 5]);
+  // one full / empty pair per accumulator (stage s, row half h): the four
+  // warps that drain an accumulator start as soon as its 8 UMMAs retire and
+  // hand it back on their own
+  auto bar_afull = [&](int s, int h) { return smem_u32(&bars[1 + 2 * SC_STAGES + s * 2 + h]); };
+  auto bar_aempty = [&](int s, int h) {
+    return smem_u32(&bars[1 + 2 * SC_STAGES + 4 + s * 2 + h]);
+  };
+  const uint32_t bar_mref = smem_u32(&bars[1 + 2 * SC_STAGES + 8]);
+  const uint32_t bar_part = smem_u32(&bars[1 + 2 * SC_STAGES + 9]);
 
   if (tid == 0) {
     abort_flag = 0;
@@ -127,10 +132,11 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
       mbar_init(bar_kfull(s), 1);
       mbar_init(bar_kempty(s), 1);
     }
-    for (int s = 0; s < 2; s++) {
-      mbar_init(bar_afull(s), 1);
-      mbar_init(bar_aempty(s), 8);  // one arrival per warp of the draining group
-    }
+    for (int s = 0; s < 2; s++)
+      for (int h = 0; h < 2; h++) {
+        mbar_init(bar_afull(s, h), 1);
+        mbar_init(bar_aempty(s, h), 4);  // one arrival per warp draining the accumulator
+      }
     mbar_init(bar_mref, 8);
     mbar_init(bar_part, 8);
     mbar_init_fence();
@@ -181,24 +187,28 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
         const uint32_t ph = (t / SC_STAGES) & 1;
         const int a = t & 1;
         const uint32_t pa = (t >> 1) & 1;
-        if (!mbar_wait(bar_aempty(a), pa ^ 1, w, FTK_DEV_TIMEOUT_MMA)) break;
         if (!mbar_wait(bar_kfull(s), ph, w, FTK_DEV_TIMEOUT_MMA)) break;
         tc_fence_after();
         const uint64_t kdesc = desc_advance(kdesc0, s * K_STAGE_BYTES);
-        if (elect_one()) {
+        bool fine = true;
 #pragma unroll
         for (int half = 0; half < 2; half++) {
-          const uint32_t d_tmem = tmem + static_cast<uint32_t>((a * 2 + half) * SC_KT);
-          const uint64_t qdesc = desc_advance(qdesc0, half * NCH * SC_CHUNK_BYTES);
+          if (!mbar_wait(bar_aempty(a, half), pa ^ 1, w, FTK_DEV_TIMEOUT_MMA)) { fine = false; break; }
+          tc_fence_after();
+          if (elect_one()) {
+            const uint32_t d_tmem = tmem + static_cast<uint32_t>((a * 2 + half) * SC_KT);
+            const uint64_t qdesc = desc_advance(qdesc0, half * NCH * SC_CHUNK_BYTES);
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ks++) {
-            const uint32_t off = (ks / 4) * SC_CHUNK_BYTES + (ks % 4) * 32;
-            umma_ss(d_tmem, desc_advance(qdesc, off), desc_advance(kdesc, off), idesc, ks > 0);
+            for (int ks = 0; ks < D / 16; ks++) {
+              const uint32_t off = (ks / 4) * SC_CHUNK_BYTES + (ks % 4) * 32;
+              umma_ss(d_tmem, desc_advance(qdesc, off), desc_advance(kdesc, off), idesc, ks > 0);
+            }
+            if (half == 1) umma_commit(bar_kempty(s));  // smem stage reusable once retired
+            umma_commit(bar_afull(a, half));             // this accumulator is readable
           }
+          __syncwarp();
         }
-        umma_commit(bar_kempty(s));  // smem stage reusable once these UMMAs retire
-        umma_commit(bar_afull(a));   // accumulators readable
-        }
+        if (!fine) break;
         __syncwarp();
       }
     }
@@ -229,7 +239,7 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     if (p.mode == 0) {
       if (group == 0) {
         // reference exponent from the row maximum over the first key tile
-        ok = mbar_wait(bar_afull(0), 0, w, FTK_DEV_TIMEOUT_CONSUMER);
+        ok = mbar_wait(bar_afull(0, half), 0, w, FTK_DEV_TIMEOUT_CONSUMER);
         if (ok) {
           tc_fence_after();
           const TileInfo ti = tile_info(p, 0);
@@ -263,23 +273,16 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
       if (tile_owner(p, t) != group) continue;
       const int a = t & 1;
       const uint32_t pa = (t >> 1) & 1;
-      if (!mbar_wait(bar_afull(a), pa, w, FTK_DEV_TIMEOUT_CONSUMER)) { ok = false; break; }
+      if (!mbar_wait(bar_afull(a, half), pa, w, FTK_DEV_TIMEOUT_CONSUMER)) { ok = false; break; }
       tc_fence_after();
       const TileInfo ti = tile_info(p, t);
       const int lo = max(0, -ti.row0), hi = min(ti.used, p.N - ti.row0);
       const bool full = (lo == 0 && hi == ti.used);
       if (ti.col_in_block0 == 0) { j = ti.block0; col_in_block = 0; }
       const uint32_t acc_addr = lane_addr + static_cast<uint32_t>((a * 2 + half) * SC_KT);
-      for (int c0 = 0; c0 < ti.used; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(acc_addr + static_cast<uint32_t>(c0), r);
-        tmem_wait_ld();
-        if (c0 + 32 >= ti.used) {
-          // last chunk of the tile is in registers: hand the accumulator back
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_aempty(a));
-        }
+      // one 32-column chunk: two 16-column halves, block sums flushed on the
+      // 16-column grid (block sizes are multiples of 16)
+      auto process = [&](const uint32_t (&r)[32], int c0) {
 #pragma unroll
         for (int hc = 0; hc < 2; hc++) {
           const int cb = c0 + hc * 16;
@@ -320,6 +323,37 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
               }
             }
           }
+        }
+      };
+      auto release = [&]() {
+        // the tile's last chunk is in registers: hand the accumulator back
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_aempty(a, half));
+      };
+      if (ti.used == SC_KT) {
+        // full tile: the load of chunk k+1 is in flight while chunk k is summed
+        uint32_t ra[32], rb[32];
+        tmem_ld32(acc_addr, ra);
+        tmem_wait_ld();
+        tmem_ld32(acc_addr + 32, rb);
+        process(ra, 0);
+        tmem_wait_ld();
+        tmem_ld32(acc_addr + 64, ra);
+        process(rb, 32);
+        tmem_wait_ld();
+        tmem_ld32(acc_addr + 96, rb);
+        process(ra, 64);
+        tmem_wait_ld();
+        release();
+        process(rb, 96);
+      } else {
+        for (int c0 = 0; c0 < ti.used; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(acc_addr + static_cast<uint32_t>(c0), r);
+          tmem_wait_ld();
+          if (c0 + 32 >= ti.used) release();
+          process(r, c0);
         }
       }
     }
