@@ -113,6 +113,114 @@ topk_select_kernel(const float* __restrict__ scores, const float* __restrict__ r
   }
 }
 
+// Register variant for M <= 32 * IPT (IPT a compile-time constant): the lane's
+// IPT averages stay in registers, so the rescan after a pop is a fully
+// unrolled compare/select chain with no shared-memory traffic, and the lane
+// caches its runner-up so that most pops need no rescan at all.  Raw scores
+// still sit in shared memory (one broadcast read per extracted element).
+template <int IPT>
+__global__ void __launch_bounds__(SEL_WARPS * 32)
+topk_select_reg_kernel(const float* __restrict__ scores, const float* __restrict__ row_scale,
+                       int64_t rows, int M, int M_out, int bsz, int pad_head, int pad_tail,
+                       float threshold, int32_t* __restrict__ out_idx,
+                       float* __restrict__ out_raw, float* __restrict__ out_avg) {
+  __shared__ float sraw_all[SEL_WARPS][32 * IPT];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * SEL_WARPS + warp;
+  if (row >= rows) return;
+  float* sraw = sraw_all[warp];
+  const float* in = scores + row * M;
+  const float inv_total = row_scale ? __frcp_rn(row_scale[row]) : 1.f;
+  const bool pow2 = (bsz & (bsz - 1)) == 0;
+  const float inv_bsz = 1.f / static_cast<float>(bsz);
+  const int NEG = __float_as_int(-1.f);
+
+  int a[IPT];   // average bit patterns (non-negative floats order as ints); NEG = absent
+#pragma unroll
+  for (int i = 0; i < IPT; i++) {
+    const int j = i * 32 + lane;
+    float raw = 0.f, avg = -1.f;
+    if (j < M) {
+      raw = in[j];
+      if (row_scale) raw *= inv_total;
+      int n = bsz;
+      if (j == 0) n -= pad_head;
+      if (j == M - 1) n -= pad_tail;
+      avg = (pow2 && n == bsz) ? raw * inv_bsz : __fdiv_rn(raw, static_cast<float>(n));
+      if (!(avg >= 0.f)) avg = 0.f;
+    }
+    sraw[j] = raw;
+    a[i] = __float_as_int(avg);
+  }
+  // best and runner-up of the lane; ties keep the lower slot (= lower id)
+  int b1 = NEG, i1 = IPT, b2 = NEG, i2 = IPT;
+  auto rescan = [&]() {
+    b1 = NEG; i1 = IPT; b2 = NEG; i2 = IPT;
+#pragma unroll
+    for (int i = 0; i < IPT; i++) {
+      const int v = a[i];
+      if (v > b1) { b2 = b1; i2 = i1; b1 = v; i1 = i; }
+      else if (v > b2) { b2 = v; i2 = i; }
+    }
+  };
+  rescan();
+  __syncwarp();
+
+  float cum = 0.f;
+  bool cut = false;
+  int32_t* oi = out_idx + row * M_out;
+  float* orw = out_raw + row * M_out;
+  float* oav = out_avg + row * M_out;
+  int hold_idx = -1;
+  float hold_raw = 0.f, hold_avg = 0.f;
+  for (int r = 0; r < M_out; r++) {
+    int w_idx = -1;
+    float w_raw = 0.f, w_avg = 0.f;
+    if (!cut) {
+      const int mx = redux_max_s32(b1);
+      const unsigned cand =
+          (b1 == mx) ? static_cast<unsigned>(i1 * 32 + lane) : 0xffffffffu;
+      const unsigned win = redux_min_u32(cand);
+      w_idx = static_cast<int>(win);
+      w_raw = sraw[win];
+      w_avg = __int_as_float(mx);
+      cum += w_raw;
+      if (cum >= threshold) cut = true;
+      if ((win & 31u) == static_cast<unsigned>(lane)) {
+        // pop: the slot is consumed; promote the runner-up, rescan only when
+        // there is none cached
+#pragma unroll
+        for (int i = 0; i < IPT; i++)
+          if (i == i1) a[i] = NEG;
+        if (i2 < IPT) {
+          b1 = b2; i1 = i2; b2 = NEG; i2 = IPT;
+        } else {
+          rescan();
+        }
+      }
+    }
+    if ((r & 31) == lane) { hold_idx = w_idx; hold_raw = w_raw; hold_avg = w_avg; }
+    if ((r & 31) == 31 || r == M_out - 1) {
+      const int base = r & ~31;
+      if (base + lane <= r) {
+        oi[base + lane] = hold_idx;
+        orw[base + lane] = hold_raw;
+        oav[base + lane] = hold_avg;
+      }
+    }
+  }
+}
+
+template <int IPT>
+static void launch_select_reg(const float* block_scores, const float* row_scale, int64_t rows,
+                              int M, int M_out, int bsz, int pad_head, int pad_tail,
+                              float threshold, int32_t* topk_idx, float* topk_raw,
+                              float* topk_avg, unsigned grid, cudaStream_t st) {
+  topk_select_reg_kernel<IPT><<<grid, SEL_WARPS * 32, 0, st>>>(
+      block_scores, row_scale, rows, M, M_out, bsz, pad_head, pad_tail, threshold, topk_idx,
+      topk_raw, topk_avg);
+}
+
 int select_launch(const float* block_scores, const float* row_scale, int64_t rows, int M,
                   int max_topk, int bsz, int pad_head, int pad_tail, float threshold,
                   int32_t* topk_idx, float* topk_raw, float* topk_avg, cudaStream_t st) {
@@ -121,18 +229,31 @@ int select_launch(const float* block_scores, const float* row_scale, int64_t row
   if (pad_head < 0 || pad_tail < 0 || pad_head >= bsz || pad_tail >= bsz) return FTK_ERR_BAD_ARG;
   if (M > 4096) return FTK_ERR_UNSUPPORTED;
   const int M_out = max_topk > 0 ? std::min(max_topk, M) : M;
-  const int Mp = (M + 31) & ~31;
-  const size_t smem = static_cast<size_t>(SEL_WARPS) * 2 * Mp * sizeof(float);
-  if (smem > 48 * 1024) {
-    if (cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem)) != cudaSuccess)
-      return FTK_ERR_CUDA;
-  }
   const int64_t grid = (rows + SEL_WARPS - 1) / SEL_WARPS;
   if (grid > 0x7fffffffLL) return FTK_ERR_BAD_ARG;
-  topk_select_kernel<<<static_cast<unsigned>(grid), SEL_WARPS * 32, smem, st>>>(
-      block_scores, row_scale, rows, M, M_out, bsz, pad_head, pad_tail, threshold, topk_idx,
-      topk_raw, topk_avg);
+  const unsigned g = static_cast<unsigned>(grid);
+#define FTK_SEL_REG(IPT)                                                                        \
+  launch_select_reg<IPT>(block_scores, row_scale, rows, M, M_out, bsz, pad_head, pad_tail,     \
+                         threshold, topk_idx, topk_raw, topk_avg, g, st)
+  if (M <= 32) FTK_SEL_REG(1);
+  else if (M <= 64) FTK_SEL_REG(2);
+  else if (M <= 128) FTK_SEL_REG(4);
+  else if (M <= 256) FTK_SEL_REG(8);
+  else if (M <= 512) FTK_SEL_REG(16);
+  else if (M <= 1024) FTK_SEL_REG(32);
+  else {
+    const int Mp = (M + 31) & ~31;
+    const size_t smem = static_cast<size_t>(SEL_WARPS) * 2 * Mp * sizeof(float);
+    if (smem > 48 * 1024) {
+      if (cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem)) != cudaSuccess)
+        return FTK_ERR_CUDA;
+    }
+    topk_select_kernel<<<g, SEL_WARPS * 32, smem, st>>>(
+        block_scores, row_scale, rows, M, M_out, bsz, pad_head, pad_tail, threshold, topk_idx,
+        topk_raw, topk_avg);
+  }
+#undef FTK_SEL_REG
   return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
 }
 
