@@ -6,10 +6,11 @@
 //
 // One CTA owns 256 query rows of one (batch, head) slice and streams every
 // key tile once.  Roles: warp 0 = TMA producer, warp 1 = UMMA issuer, warps
-// 2..9 = 256 softmax threads, one query row each (TMEM lane == row).
-// Two 128x128 fp32 accumulators per stage (rows 0-127 / 128-255 share the K
-// tile), two stages, so the tensor core works on tile t+1 while the softmax
-// threads drain tile t: 4 x 128 = 512 TMEM columns.
+// 2..17 = two groups of 256 softmax threads, one query row each (TMEM lane ==
+// row).  Two 128x128 fp32 accumulators per stage (rows 0-127 / 128-255 share
+// the K tile), two stages: 4 x 128 = 512 TMEM columns.  Group s drains stage
+// s, so the groups work concurrently on consecutive tiles while the tensor
+// core refills whichever accumulator was handed back.
 //
 // Softmax is single pass against a fixed per-row reference exponent `mref`
 // (an integer in log2 units): sum_j[t] = sum_{i in block j} 2^(c*s_ti - mref),
