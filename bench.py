@@ -210,19 +210,55 @@ def run_ours(args):
     ftk.check_errors()
 
     # ---- end to end: host buffers in, host buffers out --------------------
+    # Every step's four inputs come from pinned host memory and its four
+    # results go back to pinned host memory, all inside the timed region.  The
+    # copies run on two side streams (PCIe is full duplex) over double-buffered
+    # device inputs, so step i+1's upload and step i-1's download overlap step
+    # i's kernels; dependencies are CUDA events only.
+    cur = torch.cuda.current_stream(dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    bufs = [devt, {k: torch.empty_like(v) for k, v in devt.items()}]
+    ev_in = [torch.cuda.Event(), torch.cuda.Event()]
+    ev_done = [torch.cuda.Event(), torch.cuda.Event()]
+
+    def upload(i):
+        with torch.cuda.stream(s_in):
+            for k in host:
+                bufs[i % 2][k].copy_(host[k], non_blocking=True)
+            ev_in[i % 2].record(s_in)
+
     barrier()
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        for k in devt:
-            devt[k].copy_(host[k], non_blocking=True)
+    s_in.wait_stream(cur)
+    s_out.wait_stream(cur)
+    upload(0)
+    keep = []
+    for i in range(args.steps):
+        devt = bufs[i % 2]
+        cur.wait_event(ev_in[i % 2])
         _, res = step(False)
-        for nm, t in zip(("o", "dq", "dk", "dv"), res[:4]):
-            host_out[nm].copy_(t, non_blocking=True)
+        ev_done[i % 2].record(cur)
+        if i + 1 < args.steps:
+            if i >= 1:
+                # buffer (i+1)%2 was last read by step i-1: the copy stream
+                # must not overwrite it before that step's kernels finished
+                s_in.wait_event(ev_done[(i + 1) % 2])
+            upload(i + 1)
+        s_out.wait_event(ev_done[i % 2])
+        with torch.cuda.stream(s_out):
+            for nm, t in zip(("o", "dq", "dk", "dv"), res[:4]):
+                host_out[nm].copy_(t, non_blocking=True)
+                t.record_stream(s_out)
+        keep.append(res)
+    cur.wait_stream(s_out)
+    cur.wait_stream(s_in)
     e1.record()
     torch.cuda.synchronize()
     e2e_ms = e0.elapsed_time(e1)
+    devt = bufs[0]
+    del keep
     ftk.check_errors()
 
     if dist is not None:

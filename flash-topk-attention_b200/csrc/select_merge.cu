@@ -113,11 +113,91 @@ topk_select_kernel(const float* __restrict__ scores, const float* __restrict__ r
   }
 }
 
+// Bitonic network over 32*E values held E per lane (position p = r*32 + lane),
+// sorted largest first.  Distances below 32 exchange across lanes, the others
+// between registers of one lane; every index is a compile-time constant.
+template <int E, typename T>
+__device__ __forceinline__ void bitonic_desc(T (&v)[E], int lane) {
+  constexpr int LOGN = (E == 1 ? 5 : E == 2 ? 6 : E == 4 ? 7 : 8);
+#pragma unroll
+  for (int lk = 1; lk <= LOGN; lk++) {
+    const int k = 1 << lk;
+#pragma unroll
+    for (int lj = lk - 1; lj >= 0; lj--) {
+      const int j = 1 << lj;
+      if (j >= 32) {
+        const int jr = j >> 5;
+#pragma unroll
+        for (int r = 0; r < E; r++) {
+          if ((r & jr) == 0) {
+            const bool desc = (((r * 32) & k) == 0);
+            const T x = v[r], y = v[r | jr];
+            const bool sw = desc ? (x < y) : (x > y);
+            v[r] = sw ? y : x;
+            v[r | jr] = sw ? x : y;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < E; r++) {
+          const T o = __shfl_xor_sync(0xffffffffu, v[r], j);
+          const bool desc = (((r * 32 + lane) & k) == 0);
+          const bool lower = (lane & j) == 0;
+          const bool take_max = (desc == lower);
+          const bool o_gt = o > v[r];
+          v[r] = (take_max == o_gt) ? o : v[r];
+        }
+      }
+    }
+  }
+}
+
+// Sort the compacted candidates (64-bit keys: average bits high, inverted block
+// id low, so larger key = better score, then lower id) and write the first
+// M_out <= 32 of them.  The running sum of raw scores is accumulated in rank
+// order, one addition per rank, exactly like a sequential scan.
+template <int E>
+__device__ __forceinline__ void sorted_emit(const unsigned long long* cand, int count, int lane,
+                                            const float* sraw, int M_out, float threshold,
+                                            int32_t* oi, float* orw, float* oav) {
+  unsigned long long v[E];
+#pragma unroll
+  for (int r = 0; r < E; r++) v[r] = (r * 32 + lane < count) ? cand[r * 32 + lane] : 0ull;
+  bitonic_desc<E>(v, lane);
+  const bool mine = lane < M_out;
+  const unsigned lo = static_cast<unsigned>(v[0]);
+  const int id = static_cast<int>(0xffffffffu - lo);
+  const float avg = __int_as_float(static_cast<int>(v[0] >> 32));
+  const float raw = mine ? sraw[id] : 0.f;
+  float cum = 0.f, mycum = 0.f;
+  for (int p = 0; p < M_out; p++) {
+    cum += __shfl_sync(0xffffffffu, raw, p);
+    if (p == lane) mycum = cum;
+  }
+  const unsigned cutmask = __ballot_sync(0xffffffffu, mine && (mycum >= threshold));
+  const int cutpos = cutmask ? (__ffs(cutmask) - 1) : 32;
+  if (mine) {
+    const bool keep = lane <= cutpos;
+    oi[lane] = keep ? id : -1;
+    orw[lane] = keep ? raw : 0.f;
+    oav[lane] = keep ? avg : 0.f;
+  }
+}
+
 // Register variant for M <= 32 * IPT (IPT a compile-time constant): the lane's
 // IPT averages stay in registers, so the rescan after a pop is a fully
 // unrolled compare/select chain with no shared-memory traffic, and the lane
 // caches its runner-up so that most pops need no rescan at all.  Raw scores
 // still sit in shared memory (one broadcast read per extracted element).
+//
+// When at most 32 entries are wanted the kernel first tries a filter-and-sort
+// path: every lane splits its slots into two groups and takes each group's
+// maximum; the 64 maxima are 64 distinct entries, so the M_out-th largest of
+// them (T) is a lower bound of the M_out-th largest entry overall, and
+// {average >= T} holds every entry the result can contain (ties with T
+// included).  That set is compacted with ballots (about 40 entries for
+// M = 512), sorted as 64-bit keys and written.  The extraction loop below only
+// runs when the set does not fit 128 candidates.
 template <int IPT>
 __global__ void __launch_bounds__(SEL_WARPS * 32)
 topk_select_reg_kernel(const float* __restrict__ scores, const float* __restrict__ row_scale,
@@ -125,6 +205,7 @@ topk_select_reg_kernel(const float* __restrict__ scores, const float* __restrict
                        float threshold, int32_t* __restrict__ out_idx,
                        float* __restrict__ out_raw, float* __restrict__ out_avg) {
   __shared__ float sraw_all[SEL_WARPS][32 * IPT];
+  __shared__ unsigned long long scand_all[IPT >= 2 ? SEL_WARPS : 1][128];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * SEL_WARPS + warp;
   if (row >= rows) return;
@@ -163,14 +244,47 @@ topk_select_reg_kernel(const float* __restrict__ scores, const float* __restrict
       else if (v > b2) { b2 = v; i2 = i; }
     }
   };
-  rescan();
   __syncwarp();
-
-  float cum = 0.f;
-  bool cut = false;
   int32_t* oi = out_idx + row * M_out;
   float* orw = out_raw + row * M_out;
   float* oav = out_avg + row * M_out;
+
+  if constexpr (IPT >= 2) {
+    if (M_out <= 32) {
+      int gm[2] = {NEG, NEG};
+#pragma unroll
+      for (int i = 0; i < IPT; i++) gm[i >= IPT / 2] = max(gm[i >= IPT / 2], a[i]);
+      bitonic_desc<2>(gm, lane);
+      const int T = __shfl_sync(0xffffffffu, gm[0], M_out - 1);
+      if (T >= 0) {
+        unsigned long long* cand = scand_all[warp];
+        const unsigned lt = (1u << lane) - 1u;
+        int count = 0;
+#pragma unroll
+        for (int i = 0; i < IPT; i++) {
+          const bool c = a[i] >= T;
+          const unsigned bal = __ballot_sync(0xffffffffu, c);
+          const int pos = count + __popc(bal & lt);
+          if (c && pos < 128)
+            cand[pos] = (static_cast<unsigned long long>(static_cast<unsigned>(a[i])) << 32) |
+                        (0xffffffffu - static_cast<unsigned>(i * 32 + lane));
+          count += __popc(bal);
+        }
+        __syncwarp();
+        if (count <= 128) {
+          if (count <= 32) sorted_emit<1>(cand, count, lane, sraw, M_out, threshold, oi, orw, oav);
+          else if (count <= 64)
+            sorted_emit<2>(cand, count, lane, sraw, M_out, threshold, oi, orw, oav);
+          else sorted_emit<4>(cand, count, lane, sraw, M_out, threshold, oi, orw, oav);
+          return;
+        }
+      }
+    }
+  }
+  rescan();
+
+  float cum = 0.f;
+  bool cut = false;
   int hold_idx = -1;
   float hold_raw = 0.f, hold_avg = 0.f;
   for (int r = 0; r < M_out; r++) {

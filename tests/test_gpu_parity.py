@@ -124,6 +124,31 @@ def test_select_merge_reverse_exact(ftk, name):
     np.testing.assert_array_equal(ids.cpu().numpy(), oids)
 
 
+@pytest.mark.parametrize("M", [33, 40, 64, 100, 257, 512, 1000, 1024, 1500])
+def test_select_paths_exact(ftk, M):
+    """Every select path (filter-and-sort with 32/64/128 candidates, the
+    extraction loop behind it, the shared-memory kernel above M = 1024) against
+    the oracle: smooth rows, rows with many exact ties, rows whose threshold
+    cuts early, padded first/last blocks, flat rows (all candidates tie)."""
+    rng = np.random.default_rng(1000 + M)
+    rows = 96
+    x = rng.random((1, 2, rows, M), dtype=np.float32) ** 4
+    x[0, 0, :32] = np.round(x[0, 0, :32] * 8) / 8           # heavy ties
+    x[0, 0, 32:40] = 0.25                                    # flat: everything ties
+    x[0, 1, :16, :3] += 50.0                                 # early cut
+    x[0, 1, 16:24, ::7] = 0.0
+    x /= x.sum(-1, keepdims=True)
+    scores = torch.from_numpy(x).cuda()
+    for b, pad in ((64, (0, 0)), (48, (5, 47))):
+        for thr, k in ((0.9, 32), (0.5, 8), (0.2, 1), (1.5, 17), (0.9, 0), (0.05, 40)):
+            gi, gr, ga = ftk.flash_topk_select(scores, thr, k, b, pad)
+            oi, orw, oa = orc.topk_select(x, thr, k, b, pad)
+            np.testing.assert_array_equal(gi.cpu().numpy(), oi, err_msg=f"{M} {b} {thr} {k}")
+            np.testing.assert_array_equal(gr.cpu().numpy(), orw)
+            np.testing.assert_array_equal(ga.cpu().numpy(), oa)
+    ftk.check_errors()
+
+
 @pytest.mark.parametrize("name", list(cases.GOLDEN_CASES))
 def test_attention_fwd_bwd(ftk, name):
     cfg = cases.GOLDEN_CASES[name]
