@@ -49,6 +49,8 @@ __global__ void delta_kernel(const uint8_t* __restrict__ o, const uint8_t* __res
 
 constexpr int BW_THREADS = 576;  // 2 + 2 x 8 warps
 constexpr int BW_MAX_STAGES = 4;
+constexpr int DQ_KST = 7;        // dQ kernel: K tiles in the ring (held until dQ += dS K ran)
+constexpr int DQ_VST = 5;        // dQ kernel: V tiles in the ring (free once dP is computed)
 
 struct BwdParams {
   int N, H, QM, W, Mkv;
@@ -70,6 +72,12 @@ struct BwdParams {
 // S and dP UMMAs are read from TMEM, which leaves shared-memory bandwidth to
 // the K/V tiles), S[2] 128/192, dP[2] 256/320 (dS written over their first
 // half), dQ 384..
+// Shared memory: the Q and dO tiles are dead once they sit in TMEM, so their
+// 2 x 128 rows become four slots of the V ring (the fifth follows the K ring);
+// K has its own ring.  K and V travel in
+// separate rings because V is released after dP while K stays until dQ: the
+// producer runs several tiles ahead, which is what lets the loads overlap the
+// UMMAs instead of alternating with them.
 template <int D>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
@@ -83,9 +91,10 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = smem;
   uint8_t* sDO = smem + ROW_TILE_BYTES;
-  uint8_t* sKV = smem + 2 * ROW_TILE_BYTES;
+  uint8_t* sV = smem;                          // over Q / dO once they are in TMEM
+  uint8_t* sK = smem + 2 * ROW_TILE_BYTES;
   __shared__ UnionScratch un;
-  __shared__ __align__(8) uint64_t bars[1 + 2 * BW_MAX_STAGES + 6];
+  __shared__ __align__(8) uint64_t bars[1 + 2 * DQ_KST + 2 * DQ_VST + 6];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
 
@@ -96,25 +105,35 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int groups = min(p.G, p.QM - m0);
   const int tile_row0 = m0 * p.g - p.q_pad_head;
   const int kv_chunk_bytes = p.kvb * 128;
-  const int stage_bytes = 2 * NCH * kv_chunk_bytes;
-  const int NST = p.nstages;
+  const int tile_bytes = NCH * kv_chunk_bytes;   // one K or V tile
+  auto v_slot = [&](int sv) {
+    return sv < 4 ? smem_u32(sV) + sv * tile_bytes
+                  : smem_u32(sK) + (DQ_KST + sv - 4) * tile_bytes;
+  };
 
   const uint32_t bar_q = smem_u32(&bars[0]);
-  auto bar_kvfull = [&](int s) { return smem_u32(&bars[1 + s]); };
-  auto bar_kvempty = [&](int s) { return smem_u32(&bars[1 + BW_MAX_STAGES + s]); };
-  auto bar_afull = [&](int s) { return smem_u32(&bars[1 + 2 * BW_MAX_STAGES + s]); };
-  auto bar_dsfull = [&](int s) { return smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 2 + s]); };
+  auto bar_kfull = [&](int s) { return smem_u32(&bars[1 + s]); };
+  auto bar_kempty = [&](int s) { return smem_u32(&bars[1 + DQ_KST + s]); };
+  auto bar_vfull = [&](int s) { return smem_u32(&bars[1 + 2 * DQ_KST + s]); };
+  auto bar_vempty = [&](int s) { return smem_u32(&bars[1 + 2 * DQ_KST + DQ_VST + s]); };
+  constexpr int BAR_A0 = 1 + 2 * DQ_KST + 2 * DQ_VST;
+  auto bar_afull = [&](int s) { return smem_u32(&bars[BAR_A0 + s]); };
+  auto bar_dsfull = [&](int s) { return smem_u32(&bars[BAR_A0 + 2 + s]); };
   // arrives once, after the last UMMA of the CTA has retired
-  const uint32_t bar_final = smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 4]);
+  const uint32_t bar_final = smem_u32(&bars[BAR_A0 + 4]);
   // Q and dO copied from shared memory into TMEM by the compute warps
-  const uint32_t bar_qt = smem_u32(&bars[1 + 2 * BW_MAX_STAGES + 5]);
+  const uint32_t bar_qt = smem_u32(&bars[BAR_A0 + 5]);
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(bar_q, 1);
-    for (int s = 0; s < BW_MAX_STAGES; s++) {
-      mbar_init(bar_kvfull(s), 1);
-      mbar_init(bar_kvempty(s), 1);
+    for (int s = 0; s < DQ_KST; s++) {
+      mbar_init(bar_kfull(s), 1);
+      mbar_init(bar_kempty(s), 1);
+    }
+    for (int s = 0; s < DQ_VST; s++) {
+      mbar_init(bar_vfull(s), 1);
+      mbar_init(bar_vempty(s), 1);
     }
     for (int s = 0; s < 2; s++) {
       mbar_init(bar_afull(s), 1);
@@ -149,16 +168,20 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
         tma_load_4d(smem_u32(sDO) + c * 128 * 128, &tm_do, bar_q, c * 64, h_idx, tile_row0, b_idx);
       }
       for (int i = 0; i < n; i++) {
-        const int s = i % NST;
-        if (!mbar_wait(bar_kvempty(s), ((i / NST) & 1) ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
+        const int sk = i % DQ_KST, sv = i % DQ_VST;
         const int tok0 = static_cast<int>(un.ids[i]) * p.kvb - p.kv_pad_head;
-        const uint32_t base = smem_u32(sKV) + s * stage_bytes;
-        mbar_expect_tx(bar_kvfull(s), stage_bytes);
-        for (int c = 0; c < NCH; c++) {
-          tma_load_4d(base + c * kv_chunk_bytes, &tm_k, bar_kvfull(s), c * 64, h_idx, tok0, b_idx);
-          tma_load_4d(base + (NCH + c) * kv_chunk_bytes, &tm_v, bar_kvfull(s), c * 64, h_idx, tok0,
-                      b_idx);
-        }
+        if (!mbar_wait(bar_kempty(sk), ((i / DQ_KST) & 1) ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
+        const uint32_t kb = smem_u32(sK) + sk * tile_bytes;
+        mbar_expect_tx(bar_kfull(sk), tile_bytes);
+        for (int c = 0; c < NCH; c++)
+          tma_load_4d(kb + c * kv_chunk_bytes, &tm_k, bar_kfull(sk), c * 64, h_idx, tok0, b_idx);
+        // the V ring lies over the Q / dO tiles: wait until they sit in TMEM
+        if (i == 0 && !mbar_wait(bar_qt, 0, w, FTK_DEV_TIMEOUT_TMA)) break;
+        if (!mbar_wait(bar_vempty(sv), ((i / DQ_VST) & 1) ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
+        const uint32_t vb = v_slot(sv);
+        mbar_expect_tx(bar_vfull(sv), tile_bytes);
+        for (int c = 0; c < NCH; c++)
+          tma_load_4d(vb + c * kv_chunk_bytes, &tm_v, bar_vfull(sv), c * 64, h_idx, tok0, b_idx);
       }
     }
   } else if (warp == 1) {
@@ -166,8 +189,8 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       // the whole warp runs this path; one elected lane issues the UMMAs
       const uint32_t idesc_a = umma_idesc(128, p.kvb, p.fmt, 0, 0);
       const uint32_t idesc_b = umma_idesc(128, D, p.fmt, 0, 1);
-      const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sKV), 16, 1024);
-      const uint64_t kmn0 = smem_desc_sw128(smem_u32(sKV), kv_chunk_bytes, 1024);
+      const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sK), 16, 1024);
+      const uint64_t kmn0 = smem_desc_sw128(smem_u32(sK), kv_chunk_bytes, 1024);
       // dS column of k-step ks: each half of the kv columns is written by its
       // own warps over the dP columns those warps read (see the compute part)
       const int kh = split ? p.kvb / 32 : p.kvb / 16;
@@ -175,11 +198,12 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       bool ok = mbar_wait(bar_qt, 0, w, FTK_DEV_TIMEOUT_MMA);
       tc_fence_after();
       auto issue_a = [&](int i) -> bool {
-        const int s = i % NST;
-        if (!mbar_wait(bar_kvfull(s), (i / NST) & 1, w, FTK_DEV_TIMEOUT_MMA)) return false;
+        const int sk = i % DQ_KST, sv = i % DQ_VST;
+        if (!mbar_wait(bar_kfull(sk), (i / DQ_KST) & 1, w, FTK_DEV_TIMEOUT_MMA)) return false;
+        if (!mbar_wait(bar_vfull(sv), (i / DQ_VST) & 1, w, FTK_DEV_TIMEOUT_MMA)) return false;
         tc_fence_after();
-        const uint64_t kdesc = desc_advance(kdesc0, s * stage_bytes);
-        const uint64_t vdesc = desc_advance(kdesc, NCH * kv_chunk_bytes);
+        const uint64_t kdesc = desc_advance(kdesc0, sk * tile_bytes);
+        const uint64_t vdesc = smem_desc_sw128(v_slot(sv), 16, 1024);
         const uint32_t sb = i & 1;
         if (elect_one()) {
 #pragma unroll
@@ -194,6 +218,7 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
                   ks > 0);
         }
         umma_commit(bar_afull(sb));
+        umma_commit(bar_vempty(sv));
         }
         __syncwarp();
         return true;
@@ -201,15 +226,15 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       if (ok) ok = issue_a(0);
       if (ok && n > 1) ok = issue_a(1);
       for (int i = 0; ok && i < n; i++) {
-        const int s = i % NST, sb = i & 1;
+        const int s = i % DQ_KST, sb = i & 1;
         if (!mbar_wait(bar_dsfull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_MMA)) break;
         tc_fence_after();
-        const uint64_t kmn = desc_advance(kmn0, s * stage_bytes);
+        const uint64_t kmn = desc_advance(kmn0, s * tile_bytes);
         if (elect_one()) {
           for (int ks = 0; ks < p.kvb / 16; ks++)
             umma_ts(tmem + 384, tmem + 256 + sb * 64 + ds_col(ks), desc_advance(kmn, ks * 2048),
                     idesc_b, (i > 0) || (ks > 0));
-          umma_commit(bar_kvempty(s));
+          umma_commit(bar_kempty(s));
         }
         __syncwarp();
         if (i + 2 < n) ok = issue_a(i + 2);
@@ -760,10 +785,9 @@ extern "C" int ftk_sparse_bwd_dq(
   if ((e = encode_tmap_bnhd(&tv, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, kv_block_size)))
     return e;
   const int nch = static_cast<int>(D / 64);
-  const int stage_bytes = 2 * nch * kv_block_size * 128;
-  p.nstages = std::min(BW_MAX_STAGES, (128 * 1024) / stage_bytes);
-  if (p.nstages < 2) return FTK_ERR_UNSUPPORTED;
-  const size_t smem = 1024 + 2 * nch * 128 * 128 + static_cast<size_t>(p.nstages) * stage_bytes;
+  // four V slots lie over the Q / dO tiles, the rest of the V ring behind the K ring
+  const size_t smem = 1024 + 2 * nch * 128 * 128 +
+                      static_cast<size_t>(DQ_KST + DQ_VST - 4) * nch * kv_block_size * 128;
   dim3 grid((QM + p.G - 1) / p.G, static_cast<unsigned>(B * H));
   if (D == 64) {
     if (cudaFuncSetAttribute(sparse_bwd_dq_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,

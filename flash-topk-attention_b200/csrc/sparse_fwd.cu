@@ -21,6 +21,7 @@
 // O accumulator is then rescaled in TMEM by the row owners.
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 
 #include "attn_common.cuh"
 #include "ftk_host.cuh"
@@ -47,6 +48,8 @@ struct FwdParams {
   int64_t so_b, so_n, so_h;
   float* lse;
   int* status;
+  int* redo_out;        // pipelined kernel: one word per CTA, 1 = redo with the exact kernel
+  const int* redo_in;   // exact kernel: when set, CTAs whose word is 0 return at once
 };
 
 template <int D>
@@ -66,6 +69,7 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   __shared__ int abort_flag;
   __shared__ float s_m[2][128], s_l[2][128];
 
+  if (p.redo_in && p.redo_in[blockIdx.y * gridDim.x + blockIdx.x] == 0) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int m0 = blockIdx.x * p.G;
   const int bh = blockIdx.y;
@@ -440,6 +444,26 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
+}  // namespace ftk
+
+#include "sparse_fwd_pipe.cuh"
+
+namespace ftk {
+
+template <int D>
+static int launch_fwd_pipe(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                           const FwdParams& p, int64_t BH, cudaStream_t st) {
+  constexpr int NCH = D / 64;
+  const size_t smem = 1024 + NCH * 128 * 128 +
+                      static_cast<size_t>(FP_KST + FP_VST) * NCH * 64 * 128;
+  if (cudaFuncSetAttribute(sparse_fwd_pipe_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return FTK_ERR_CUDA;
+  dim3 grid((p.QM + p.G - 1) / p.G, static_cast<unsigned>(BH));
+  sparse_fwd_pipe_kernel<D><<<grid, FP_THREADS, smem, st>>>(tq, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+}
+
 template <int D>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                       FwdParams p, int64_t BH, cudaStream_t st) {
@@ -461,13 +485,21 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 
 using namespace ftk;
 
+// One redo word per CTA of the pipelined kernel.
+extern "C" size_t ftk_sparse_fwd_workspace(int64_t B, int64_t H, int QM, int q_block_size) {
+  if (B <= 0 || H <= 0 || QM <= 0 || q_block_size <= 0) return 0;
+  const int G = std::max(1, std::min(AT_MAX_GROUPS, 128 / q_block_size));
+  return static_cast<size_t>(B * H) * ((QM + G - 1) / G) * sizeof(int32_t);
+}
+
 extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int dtype, int64_t B,
                               int64_t H, int64_t N, int64_t D, int64_t sq_b, int64_t sq_n,
                               int64_t sq_h, int64_t sk_b, int64_t sk_n, int64_t sk_h, int64_t sv_b,
                               int64_t sv_n, int64_t sv_h, const int32_t* merged_idx, int QM, int W,
                               int q_block_size, int kv_block_size, int q_pad_head, int kv_pad_head,
                               float scale, void* o, int64_t so_b, int64_t so_n, int64_t so_h,
-                              float* lse, int32_t* status, void* stream) {
+                              float* lse, void* workspace, size_t workspace_bytes,
+                              int32_t* status, void* stream) {
   if (!q || !k || !v || !merged_idx || !o || !lse) return FTK_ERR_BAD_ARG;
   if (B <= 0 || H <= 0 || N <= 0 || QM <= 0 || W <= 0) return FTK_ERR_BAD_ARG;
   if (dtype != FTK_DTYPE_F16 && dtype != FTK_DTYPE_BF16) return FTK_ERR_BAD_ARG;
@@ -514,6 +546,21 @@ extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int d
   e = encode_tmap_bnhd(&tv, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, kv_block_size);
   if (e) return e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // bf16, 64-row kv blocks, q-blocks of 64 or 128 rows and a workspace: the
+  // pipelined kernel runs first and the exact kernel redoes the CTAs it flags.
+  const char* env = getenv("FTK_FWD_PIPE");
+  const bool pipe = dtype == FTK_DTYPE_BF16 && kv_block_size == 64 &&
+                    (q_block_size == 64 || q_block_size == 128) && workspace &&
+                    workspace_bytes >= ftk_sparse_fwd_workspace(B, H, QM, q_block_size) &&
+                    !(env && env[0] == '0');
+  if (pipe) {
+    p.redo_out = static_cast<int*>(workspace);
+    e = (D == 64) ? launch_fwd_pipe<64>(tq, tk, tv, p, B * H, st)
+                  : launch_fwd_pipe<128>(tq, tk, tv, p, B * H, st);
+    if (e) return e;
+    p.redo_out = nullptr;
+    p.redo_in = static_cast<const int*>(workspace);
+  }
   if (D == 64) return launch_fwd<64>(tq, tk, tv, p, B * H, st);
   return launch_fwd<128>(tq, tk, tv, p, B * H, st);
 }

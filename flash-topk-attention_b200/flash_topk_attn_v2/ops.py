@@ -430,13 +430,17 @@ class FlashSparseAttnFunc(torch.autograd.Function):
         QM, W = merged.shape[2], merged.shape[3]
         o = torch.empty(B, N, C, dtype=q.dtype, device=dev)
         lse = torch.empty(B, H, N, dtype=torch.float32, device=dev)
+        ws_bytes = int(lib.ftk_sparse_fwd_workspace(B, H, QM, q_block_size))
+        ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
         _call("ftk_sparse_fwd", lib.ftk_sparse_fwd, 
             ptr(qq), ptr(kk), ptr(vv), _lib.dtype_code(qq), B, H, N, D,
             sq_b, sq_n, sq_h, sk_b, sk_n, sk_h, sv_b, sv_n, sv_h,
             ptr(merged), QM, W, q_block_size, kv_block_size, q_pad_head, kv_pad_head,
-            float(scale), ptr(o), N * C, C, D, ptr(lse), ptr(status_word(dev)),
-            stream_ptr(dev))
-        _count(1)
+            float(scale), ptr(o), N * C, C, D, ptr(lse), ptr(ws), ws_bytes,
+            ptr(status_word(dev)), stream_ptr(dev))
+        piped = (q.dtype == torch.bfloat16 and kv_block_size == 64
+                 and q_block_size in (64, 128) and os.environ.get("FTK_FWD_PIPE", "1")[:1] != "0")
+        _count(2 if piped else 1)
         _after(dev)
         ctx.save_for_backward(qq, kk, vv, o, lse, merged)
         ctx.meta = (H, D, q_block_size, kv_block_size, float(scale), q_pad_head, kv_pad_head,

@@ -180,13 +180,21 @@ int ftk_sort_by_count(const int32_t* counts, int64_t total, int max_count,
  * query row of q-block m attends to the tokens of the blocks listed in the
  * valid prefix of its row.  o in `dtype` with strides (so_*), lse fp32
  * [B*H][N] (natural log; -inf and o = 0 for an empty list).
- */
+ * `workspace` (ftk_sparse_fwd_workspace bytes, may be NULL) enables the
+ * pipelined kernel for bf16 / 64-row kv blocks / q-blocks of 64 or 128 rows:
+ * it uses one fixed reference exponent per row, and the exact running-maximum
+ * kernel, launched behind it, recomputes the tiles whose scores left the safe
+ * exponent range (none on ordinary inputs).  Without a workspace only the
+ * exact kernel runs.  Setting the environment variable FTK_FWD_PIPE=0 does the
+ * same. */
+size_t ftk_sparse_fwd_workspace(int64_t B, int64_t H, int QM, int q_block_size);
 int ftk_sparse_fwd(const void* q, const void* k, const void* v, int dtype, int64_t B, int64_t H,
                    int64_t N, int64_t D, int64_t sq_b, int64_t sq_n, int64_t sq_h, int64_t sk_b,
                    int64_t sk_n, int64_t sk_h, int64_t sv_b, int64_t sv_n, int64_t sv_h,
                    const int32_t* merged_idx, int QM, int W, int q_block_size, int kv_block_size,
                    int q_pad_head, int kv_pad_head, float scale, void* o, int64_t so_b,
-                   int64_t so_n, int64_t so_h, float* lse, int32_t* status, void* stream);
+                   int64_t so_n, int64_t so_h, float* lse, void* workspace, size_t workspace_bytes,
+                   int32_t* status, void* stream);
 
 /* Replaces preprocess_delta (flash_topk_attn_v2/sparse_attn_bwd.py:12-33) and
  * sparse_attn_bwd_dq_launch (csrc/sparse_attn_bwd_dq.cpp:3-15,

@@ -214,6 +214,81 @@ def test_attention_empty_and_partial_lists(ftk):
     _close(v.grad.float().cpu().numpy(), wv, what="dV")
 
 
+def _random_lists(rng, BH, QM, M, width, empty_every=5):
+    merged = np.full((BH, QM, width), -1, dtype=np.int32)
+    for i in range(BH):
+        for m in range(QM):
+            if (i + m) % empty_every == empty_every - 1:
+                continue
+            c = int(rng.integers(1, min(width, M) + 1))
+            merged[i, m, :c] = rng.permutation(M)[:c]
+    return merged
+
+
+@pytest.mark.parametrize("g,D,N,qpad,kvpad", [
+    (64, 128, 1000, (24, 0), (20, 4)),
+    (64, 128, 1024, (0, 0), (0, 0)),
+    (64, 64, 777, (0, 55), (0, 55)),
+])
+def test_fwd_pipelined_kernel(ftk, g, D, N, qpad, kvpad, monkeypatch):
+    """bf16 / 64-row kv blocks take the pipelined forward kernel (fixed
+    reference exponent, four tiles in flight).  Ragged lengths, virtual
+    padding, empty and unequal neighbouring lists against the oracle, and
+    against the exact kernel alone (FTK_FWD_PIPE=0)."""
+    H, kvb = 3, 64
+    cfg = dict(B=2, N=N, H=H, D=D, dtype="bf16", seed=11, do_seed=12)
+    t = cases.make_inputs(cfg)
+    x = {k: v.float().numpy() for k, v in t.items()}
+    QM = (qpad[0] + N + qpad[1]) // g
+    M = (kvpad[0] + N + kvpad[1]) // kvb
+    merged = _random_lists(np.random.default_rng(5), 2 * H, QM, M, 12).reshape(2, H, QM, 12)
+    args = (t["q"].cuda(), t["k"].cuda(), t["v"].cuda(), torch.from_numpy(merged).cuda(), None,
+            H, g, kvb)
+    o, lse = ftk.flash_topk_attn(*args, kv_padding=kvpad, q_padding=qpad)
+    ftk.check_errors()
+    wo, wl = orc.sparse_attn_fwd(x["q"], x["k"], x["v"], merged, H, g, kvb, None, qpad, kvpad)
+    _close(o.float().cpu().numpy(), wo, what="O")
+    _close(lse.cpu().numpy(), wl, what="lse")
+    monkeypatch.setenv("FTK_FWD_PIPE", "0")
+    o2, lse2 = ftk.flash_topk_attn(*args, kv_padding=kvpad, q_padding=qpad)
+    ftk.check_errors()
+    _close(o.float().cpu().numpy(), o2.float().cpu().numpy(), what="O pipelined vs exact")
+    _close(lse.cpu().numpy(), lse2.cpu().numpy(), atol=1e-4, rtol=1e-5, what="lse vs exact")
+
+
+def test_fwd_pipelined_redo_on_exponent_range(ftk, monkeypatch):
+    """Later blocks beat a row's first block by far more than 2^80: the
+    pipelined kernel flags those tiles and the exact kernel redoes them, so
+    the flagged tiles equal the exact kernel's output bit for bit."""
+    H, g, kvb, N, D = 2, 64, 64, 512, 128
+    cfg = dict(B=1, N=N, H=H, D=D, dtype="bf16", seed=21, do_seed=22)
+    t = cases.make_inputs(cfg)
+    t["k"][:, 256:] *= 30.0             # logits of blocks 4..7 reach hundreds of nats
+    t["q"] *= 2.0
+    x = {k: v.float().numpy() for k, v in t.items()}
+    QM = M = N // 64
+    merged = np.tile(np.arange(M, dtype=np.int32), (1, H, QM, 1))
+    merged[0, 1, :4, 4:] = -1           # head 1, first two tiles: only the tame blocks
+    args = (t["q"].cuda(), t["k"].cuda(), t["v"].cuda(), torch.from_numpy(merged).cuda(), None,
+            H, g, kvb)
+    o, lse = ftk.flash_topk_attn(*args)
+    ftk.check_errors()
+    wo, wl = orc.sparse_attn_fwd(x["q"], x["k"], x["v"], merged, H, g, kvb)
+    assert np.abs(wl).max() > 100.0
+    assert torch.isfinite(o).all() and torch.isfinite(lse).all()
+    # one-hot softmax rows: the error is the bf16 rounding of two competing P
+    _close(o.float().cpu().numpy(), wo, atol=2e-2, what="O")
+    _close(lse.cpu().numpy(), wl, what="lse")
+    monkeypatch.setenv("FTK_FWD_PIPE", "0")
+    o2, lse2 = ftk.flash_topk_attn(*args)
+    wild = np.ones((H, N), dtype=bool)
+    wild[1, :256] = False
+    wild = torch.from_numpy(wild).cuda()
+    o4, o24 = o.view(1, N, H, D).permute(0, 2, 1, 3)[0], o2.view(1, N, H, D).permute(0, 2, 1, 3)[0]
+    assert torch.equal(o4[wild], o24[wild]) and torch.equal(lse[0][wild], lse2[0][wild])
+    _close(o.float().cpu().numpy(), o2.float().cpu().numpy(), what="O vs exact")
+
+
 def test_score_overflow_fallback(ftk):
     """Logits far above the first key tile's maximum overflow the single-pass
     sums; the exact two-pass fallback must take over."""
