@@ -193,8 +193,12 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       const uint64_t kmn0 = smem_desc_sw128(smem_u32(sK), kv_chunk_bytes, 1024);
       // dS column of k-step ks: each half of the kv columns is written by its
       // own warps over the dP columns those warps read (see the compute part)
-      const int kh = split ? p.kvb / 32 : p.kvb / 16;
-      auto ds_col = [&](int ks) { return (ks / kh) * (p.kvb / 2) + (ks % kh) * 8; };
+      // (kh is 1 or 2: shifts and masks only, the single issuing thread must
+      // not spend longer between two UMMAs than the tensor core needs for one)
+      const int kh = p.kvb / 32, kh_shift = kh >> 1, half_cols = p.kvb / 2;
+      auto ds_col = [&](int ks) {
+        return split ? (ks >> kh_shift) * half_cols + (ks & (kh - 1)) * 8 : ks * 8;
+      };
       bool ok = mbar_wait(bar_qt, 0, w, FTK_DEV_TIMEOUT_MMA);
       tc_fence_after();
       auto issue_a = [&](int i) -> bool {
@@ -505,8 +509,10 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
       const uint64_t qmn0 = smem_desc_sw128(smem_u32(sQD), q_chunk_bytes, 1024);
       // P^T / dS^T column of k-step ks: each half of the q columns is written
       // by its own warps over the columns those warps read
-      const int kh = split ? p.g / 32 : p.g / 16;
-      auto pt_col = [&](int ks) { return (ks / kh) * (p.g / 2) + (ks % kh) * 8; };
+      const int kh = p.g / 32, kh_shift = kh >> 1, half_cols = p.g / 2;
+      auto pt_col = [&](int ks) {
+        return split ? (ks >> kh_shift) * half_cols + (ks & (kh - 1)) * 8 : ks * 8;
+      };
       bool ok = mbar_wait(bar_kv, 0, w, FTK_DEV_TIMEOUT_MMA);
       auto issue_a = [&](int i) -> bool {
         const int s = i % NST;
