@@ -85,6 +85,36 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   }
 }
 
+// Wait for N barriers at once.  A test of a barrier that has already completed
+// still takes about 110 cycles to answer, so the tests are issued back to back
+// and answered together instead of one after the other.  Same bounds and abort
+// behaviour as mbar_wait.  A caller with fewer than N barriers repeats one.
+template <int N>
+__device__ __forceinline__ bool mbar_wait_all(const uint32_t (&bar)[N], const uint32_t (&parity)[N],
+                                              const WaitCtx& w, int code) {
+  uint32_t pending = (1u << N) - 1u;
+  long long t0 = 0;
+  uint32_t it = 0;
+  while (true) {
+    uint32_t got[N];
+#pragma unroll
+    for (int k = 0; k < N; k++) got[k] = ((pending >> k) & 1u) ? mbar_try(bar[k], parity[k]) : 1u;
+#pragma unroll
+    for (int k = 0; k < N; k++)
+      if (got[k]) pending &= ~(1u << k);
+    if (pending == 0u) return true;
+    if (it == 0u) t0 = clock64();
+    if (((++it) & 127u) == 0u) {
+      if (*w.abort_flag) return false;
+      if (clock64() - t0 > FTK_WAIT_CYCLES) {
+        *w.abort_flag = 1;
+        atomicCAS(w.status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
 // ----------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -201,15 +201,18 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       };
       bool ok = mbar_wait(bar_qt, 0, w, FTK_DEV_TIMEOUT_MMA);
       tc_fence_after();
-      auto issue_a = [&](int i) -> bool {
+      // The tensor core runs dry whenever the issuing thread waits, so every
+      // barrier of a round is waited for first and the round's UMMAs (dQ of
+      // tile i, then S and dP of tile i + 2) go out as one uninterrupted batch.
+      auto wait_kv = [&](int i) -> bool {
+        return mbar_wait(bar_kfull(i % DQ_KST), (i / DQ_KST) & 1, w, FTK_DEV_TIMEOUT_MMA) &&
+               mbar_wait(bar_vfull(i % DQ_VST), (i / DQ_VST) & 1, w, FTK_DEV_TIMEOUT_MMA);
+      };
+      auto mma_a = [&](int i) {   // elected lane only
         const int sk = i % DQ_KST, sv = i % DQ_VST;
-        if (!mbar_wait(bar_kfull(sk), (i / DQ_KST) & 1, w, FTK_DEV_TIMEOUT_MMA)) return false;
-        if (!mbar_wait(bar_vfull(sv), (i / DQ_VST) & 1, w, FTK_DEV_TIMEOUT_MMA)) return false;
-        tc_fence_after();
         const uint64_t kdesc = desc_advance(kdesc0, sk * tile_bytes);
         const uint64_t vdesc = smem_desc_sw128(v_slot(sv), 16, 1024);
         const uint32_t sb = i & 1;
-        if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < D / 16; ks++) {
           const uint32_t koff = (ks / 4) * kv_chunk_bytes + (ks % 4) * 32;
@@ -223,25 +226,46 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
         umma_commit(bar_afull(sb));
         umma_commit(bar_vempty(sv));
-        }
-        __syncwarp();
-        return true;
       };
-      if (ok) ok = issue_a(0);
-      if (ok && n > 1) ok = issue_a(1);
-      for (int i = 0; ok && i < n; i++) {
+      auto mma_b = [&](int i) {   // elected lane only
         const int s = i % DQ_KST, sb = i & 1;
-        if (!mbar_wait(bar_dsfull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_MMA)) break;
-        tc_fence_after();
         const uint64_t kmn = desc_advance(kmn0, s * tile_bytes);
-        if (elect_one()) {
+        if (p.kvb == 64) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ks++)
+            umma_ts(tmem + 384, tmem + 256 + sb * 64 + (ks >> 1) * 32 + (ks & 1) * 8,
+                    desc_advance(kmn, ks * 2048), idesc_b, (i > 0) || (ks > 0));
+        } else {
           for (int ks = 0; ks < p.kvb / 16; ks++)
             umma_ts(tmem + 384, tmem + 256 + sb * 64 + ds_col(ks), desc_advance(kmn, ks * 2048),
                     idesc_b, (i > 0) || (ks > 0));
-          umma_commit(bar_kempty(s));
+        }
+        umma_commit(bar_kempty(s));
+      };
+      if (ok) ok = wait_kv(0);
+      if (ok && n > 1) ok = wait_kv(1);
+      tc_fence_after();
+      if (ok && elect_one()) {
+        mma_a(0);
+        if (n > 1) mma_a(1);
+      }
+      __syncwarp();
+      for (int i = 0; ok && i < n; i++) {
+        const bool more = i + 2 < n;
+        const int i2 = more ? i + 2 : i;   // last rounds: the dS barrier stands in
+        const uint32_t wb[3] = {bar_dsfull(i & 1),
+                                more ? bar_kfull(i2 % DQ_KST) : bar_dsfull(i & 1),
+                                more ? bar_vfull(i2 % DQ_VST) : bar_dsfull(i & 1)};
+        const uint32_t wp[3] = {static_cast<uint32_t>((i >> 1) & 1),
+                                static_cast<uint32_t>(more ? (i2 / DQ_KST) & 1 : (i >> 1) & 1),
+                                static_cast<uint32_t>(more ? (i2 / DQ_VST) & 1 : (i >> 1) & 1)};
+        if (!mbar_wait_all<3>(wb, wp, w, FTK_DEV_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        if (elect_one()) {
+          mma_b(i);
+          if (i + 2 < n) mma_a(i + 2);
         }
         __syncwarp();
-        if (i + 2 < n) ok = issue_a(i + 2);
       }
       if (ok && elect_one()) umma_commit(bar_final);
       __syncwarp();
@@ -514,14 +538,14 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
         return split ? (ks >> kh_shift) * half_cols + (ks & (kh - 1)) * 8 : ks * 8;
       };
       bool ok = mbar_wait(bar_kv, 0, w, FTK_DEV_TIMEOUT_MMA);
-      auto issue_a = [&](int i) -> bool {
+      auto wait_q = [&](int i) -> bool {
+        return mbar_wait(bar_qfull(i % NST), (i / NST) & 1, w, FTK_DEV_TIMEOUT_MMA);
+      };
+      auto mma_a = [&](int i) {   // elected lane only
         const int s = i % NST;
-        if (!mbar_wait(bar_qfull(s), (i / NST) & 1, w, FTK_DEV_TIMEOUT_MMA)) return false;
-        tc_fence_after();
         const uint64_t qdesc = desc_advance(qdesc0, s * stage_bytes);
         const uint64_t dodesc = desc_advance(qdesc, NCH * q_chunk_bytes);
         const uint32_t sb = i & 1;
-        if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < D / 16; ks++) {
           const uint32_t aoff = (ks / 4) * 128 * 128 + (ks % 4) * 32;
@@ -537,30 +561,52 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
                   idesc_a, ks > 0);
         }
         umma_commit(bar_afull(sb));
-        }
-        __syncwarp();
-        return true;
       };
-      if (ok) ok = issue_a(0);
-      if (ok && n > 1) ok = issue_a(1);
-      for (int i = 0; ok && i < n; i++) {
+      auto mma_b = [&](int i) {   // elected lane only
         const int s = i % NST, sb = i & 1;
-        if (!mbar_wait(bar_pfull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_MMA)) break;
-        tc_fence_after();
         const uint64_t qmn = desc_advance(qmn0, s * stage_bytes);
         const uint64_t domn = desc_advance(qmn, NCH * q_chunk_bytes);
-        if (elect_one()) {
-        for (int ks = 0; ks < p.g / 16; ks++) {
-          const bool acc = (i > 0) || (ks > 0);
-          umma_ts(tmem + 256, tmem + sb * 64 + pt_col(ks), desc_advance(domn, ks * 2048), idesc_b,
-                  acc);
-          umma_ts(tmem + 384, tmem + 128 + sb * 64 + pt_col(ks), desc_advance(qmn, ks * 2048),
-                  idesc_b, acc);
+        if (p.g == 64) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ks++) {
+            const bool acc = (i > 0) || (ks > 0);
+            const uint32_t col = sb * 64 + (ks >> 1) * 32 + (ks & 1) * 8;
+            umma_ts(tmem + 256, tmem + col, desc_advance(domn, ks * 2048), idesc_b, acc);
+            umma_ts(tmem + 384, tmem + 128 + col, desc_advance(qmn, ks * 2048), idesc_b, acc);
+          }
+        } else {
+          for (int ks = 0; ks < p.g / 16; ks++) {
+            const bool acc = (i > 0) || (ks > 0);
+            umma_ts(tmem + 256, tmem + sb * 64 + pt_col(ks), desc_advance(domn, ks * 2048),
+                    idesc_b, acc);
+            umma_ts(tmem + 384, tmem + 128 + sb * 64 + pt_col(ks), desc_advance(qmn, ks * 2048),
+                    idesc_b, acc);
+          }
         }
         umma_commit(bar_qempty(s));
-        }
+      };
+      if (ok) ok = wait_q(0);
+      if (ok && n > 1) ok = wait_q(1);
+      tc_fence_after();
+      if (ok && elect_one()) {
+        mma_a(0);
+        if (n > 1) mma_a(1);
+      }
+      __syncwarp();
+      // The Q / dO ring is only as deep as the tiles in flight, so the next
+      // tile's loads are often still on their way: dV / dK of tile i go out
+      // first and the wait for tile i + 2 runs under them.
+      for (int i = 0; ok && i < n; i++) {
+        if (!mbar_wait(bar_pfull(i & 1), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        if (elect_one()) mma_b(i);
         __syncwarp();
-        if (i + 2 < n) ok = issue_a(i + 2);
+        if (i + 2 < n) {
+          if (!wait_q(i + 2)) break;
+          tc_fence_after();
+          if (elect_one()) mma_a(i + 2);
+          __syncwarp();
+        }
       }
       if (ok && elect_one()) umma_commit(bar_final);
       __syncwarp();

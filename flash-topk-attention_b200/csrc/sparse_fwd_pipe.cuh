@@ -175,33 +175,47 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
       const uint64_t vdesc0 = smem_desc_sw128(smem_u32(sV), CHUNK, 1024);
       bool ok = mbar_wait(bar_qt, 0, w, FTK_DEV_TIMEOUT_MMA);
       tc_fence_after();
-      // S = Q K^T for K entry j into S buffer `buf`; Q read from TMEM
-      auto issue_s = [&](int j, int buf) -> bool {
+      // The tensor core runs dry whenever the issuing thread waits, so every
+      // barrier of a round is waited for first and the round's UMMAs (P V of
+      // tile i, then S of tile i + 4) go out as one uninterrupted batch.
+      auto wait_k = [&](int j) -> bool {
+        return mbar_wait(bar_kfull(j % FP_KST), (j / FP_KST) & 1, w, FTK_DEV_TIMEOUT_MMA);
+      };
+      // S = Q K^T for K entry j into S buffer `buf`; Q read from TMEM (elected lane only)
+      auto mma_s = [&](int j, int buf) {
         const int s = j % FP_KST;
-        if (!mbar_wait(bar_kfull(s), (j / FP_KST) & 1, w, FTK_DEV_TIMEOUT_MMA)) return false;
-        tc_fence_after();
         const uint64_t kdesc = desc_advance(kdesc0, s * TILE);
         const uint32_t d_tmem = tmem + FP_COL_S + buf * 64;
-        if (elect_one()) {
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ks++)
-            umma_ts(d_tmem, tmem + ks * 8, desc_advance(kdesc, (ks / 4) * CHUNK + (ks % 4) * 32),
-                    idesc_s, ks > 0);
-          umma_commit(bar_sfull(buf));
-          umma_commit(bar_kempty(s));
-        }
-        __syncwarp();
-        return true;
+        for (int ks = 0; ks < D / 16; ks++)
+          umma_ts(d_tmem, tmem + ks * 8, desc_advance(kdesc, (ks / 4) * CHUNK + (ks % 4) * 32),
+                  idesc_s, ks > 0);
+        umma_commit(bar_sfull(buf));
+        umma_commit(bar_kempty(s));
       };
-      for (int e = 0; ok && e < npro; e++) ok = issue_s(e, e);
-      if (ok) ok = mbar_wait(bar_pro, 0, w, FTK_DEV_TIMEOUT_MMA);
+      for (int e = 0; ok && e < npro; e++) ok = wait_k(e);
       tc_fence_after();
-      for (int i = 0; ok && i < FP_GROUPS && i < n; i++) ok = issue_s(npro + i, i);
+      if (ok && elect_one())
+        for (int e = 0; e < npro; e++) mma_s(e, e);
+      __syncwarp();
+      if (ok) ok = mbar_wait(bar_pro, 0, w, FTK_DEV_TIMEOUT_MMA);
+      for (int i = 0; ok && i < FP_GROUPS && i < n; i++) ok = wait_k(npro + i);
+      tc_fence_after();
+      if (ok && elect_one())
+        for (int i = 0; i < FP_GROUPS && i < n; i++) mma_s(npro + i, i);
+      __syncwarp();
       for (int i = 0; ok && i < n; i++) {
         const int j = npro + i;
         const int s = i % FP_VST, sb = i & (FP_GROUPS - 1);
-        if (!mbar_wait(bar_vfull(s), (i / FP_VST) & 1, w, FTK_DEV_TIMEOUT_MMA) ||
-            !mbar_wait(bar_pfull(sb), (i / FP_GROUPS) & 1, w, FTK_DEV_TIMEOUT_MMA)) {
+        const bool more = i + FP_GROUPS < n;
+        const int j4 = j + FP_GROUPS;
+        const uint32_t wb[3] = {bar_vfull(s), bar_pfull(sb),
+                                more ? bar_kfull(j4 % FP_KST) : bar_pfull(sb)};
+        const uint32_t wp[3] = {static_cast<uint32_t>((i / FP_VST) & 1),
+                                static_cast<uint32_t>((i / FP_GROUPS) & 1),
+                                static_cast<uint32_t>(more ? (j4 / FP_KST) & 1
+                                                           : (i / FP_GROUPS) & 1)};
+        if (!mbar_wait_all<3>(wb, wp, w, FTK_DEV_TIMEOUT_MMA)) {
           ok = false;
           break;
         }
@@ -213,10 +227,10 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
             umma_ts(tmem + FP_COL_O, tmem + FP_COL_S + sb * 64 + ks * 8,
                     desc_advance(vdesc, ks * 2048), idesc_pv, (i > 0) || (ks > 0));
           umma_commit(bar_vempty(s));
+          // S(i+4) lands on the columns PV(i) reads P from; UMMAs run in issue order
+          if (i + FP_GROUPS < n) mma_s(j + FP_GROUPS, sb);
         }
         __syncwarp();
-        // S(i+4) lands on the columns PV(i) reads P from; UMMAs run in issue order
-        if (i + FP_GROUPS < n) ok = issue_s(j + FP_GROUPS, sb);
       }
       if (ok && elect_one()) umma_commit(bar_final);
       __syncwarp();
