@@ -188,15 +188,17 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
         const uint32_t ph = (t / SC_STAGES) & 1;
         const int a = t & 1;
         const uint32_t pa = (t >> 1) & 1;
-        if (!mbar_wait(bar_kfull(s), ph, w, FTK_DEV_TIMEOUT_MMA)) break;
+        // the three barriers of a tile are waited for together (a test of a
+        // completed barrier still takes ~110 cycles) and the tile's UMMAs go
+        // out as one batch, so the tensor core is not left idle in between
+        const uint32_t wb[3] = {bar_kfull(s), bar_aempty(a, 0), bar_aempty(a, 1)};
+        const uint32_t wp[3] = {ph, pa ^ 1, pa ^ 1};
+        if (!mbar_wait_all<3>(wb, wp, w, FTK_DEV_TIMEOUT_MMA)) break;
         tc_fence_after();
         const uint64_t kdesc = desc_advance(kdesc0, s * K_STAGE_BYTES);
-        bool fine = true;
+        if (elect_one()) {
 #pragma unroll
-        for (int half = 0; half < 2; half++) {
-          if (!mbar_wait(bar_aempty(a, half), pa ^ 1, w, FTK_DEV_TIMEOUT_MMA)) { fine = false; break; }
-          tc_fence_after();
-          if (elect_one()) {
+          for (int half = 0; half < 2; half++) {
             const uint32_t d_tmem = tmem + static_cast<uint32_t>((a * 2 + half) * SC_KT);
             const uint64_t qdesc = desc_advance(qdesc0, half * NCH * SC_CHUNK_BYTES);
 #pragma unroll
@@ -207,9 +209,7 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
             if (half == 1) umma_commit(bar_kempty(s));  // smem stage reusable once retired
             umma_commit(bar_afull(a, half));             // this accumulator is readable
           }
-          __syncwarp();
         }
-        if (!fine) break;
         __syncwarp();
       }
     }
