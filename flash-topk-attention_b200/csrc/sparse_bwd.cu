@@ -5,9 +5,11 @@
 // sparse_attn_bwd_dkv_sorted_kernel (csrc/sparse_attn_bwd_dkv_kernel.cu:6-435).
 //
 // Both kernels use the 128-row union tiles of attn_common.cuh and the same
-// three roles as the forward (TMA producer warp, UMMA issuer warp, 128 compute
-// threads owning one TMEM lane each).  With P = 2^(c S - lse2):
-//   dQ  kernel, per candidate KV block:  S = Q K^T, dP = dO V^T  (SS UMMAs),
+// three roles as the forward: TMA producer warp, UMMA issuer warp, and 16
+// compute warps in two groups (one per S / dP buffer); inside a group two
+// warps share each TMEM lane quarter and take half of a tile's columns each.
+// With P = 2^(c S - lse2):
+//   dQ  kernel, per candidate KV block:  S = Q K^T, dP = dO V^T  (Q, dO in TMEM),
 //        dS = P (dP - delta) rounded to the I/O dtype in TMEM, dQ += dS K
 //        (A from TMEM, K read MN-major from the tile that fed S).
 //   dKV kernel, per q-block of the reverse list: S^T = K Q^T, dP^T = V dO^T,

@@ -3,6 +3,11 @@
 // Replaces sparse_attn_fwd_kernel of the reference
 // (flash_topk_attn_v2/csrc/sparse_attn_kernel.cu:6-365).
 //
+// Two kernels: the exact running-maximum kernel below (every supported shape
+// and dtype) and the pipelined fixed-reference kernel of sparse_fwd_pipe.cuh
+// (bf16, 64-row kv blocks), which ftk_sparse_fwd launches first when the
+// caller passes a workspace; the exact kernel then only redoes flagged CTAs.
+//
 // One CTA owns 128 consecutive virtual query rows = G q-blocks of one (batch,
 // head) slice and walks the union of their candidate KV blocks in ascending
 // order (see attn_common.cuh).  Roles: warp 0 = TMA producer (Q once, then a

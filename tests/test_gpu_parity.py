@@ -28,15 +28,22 @@ def ftk():
     return m
 
 
-def _close(got, want, atol=ATOL, rtol=RTOL, what=""):
+def _close(got, want, atol=ATOL, rtol=RTOL, what="", stragglers=0.0):
+    """|got - want| <= atol + rtol |want| everywhere.  `stragglers` > 0 (used
+    only for bf16 gradients over very short lists, where three bf16 roundings
+    in a row are not averaged out) lets that fraction of the elements exceed
+    the bound, none of them by more than a factor of two."""
     got = np.asarray(got, dtype=np.float64)
     want = np.asarray(want, dtype=np.float64)
     fin = np.isfinite(want)
     assert (np.isfinite(got) == fin).all(), f"{what}: finiteness differs"
     assert (got[~fin] == want[~fin]).all(), what
     err = np.abs(got[fin] - want[fin])
-    bad = err > atol + rtol * np.abs(want[fin])
-    assert not bad.any(), f"{what}: {int(bad.sum())} bad, max err {float(err.max()):.3e}"
+    tol = atol + rtol * np.abs(want[fin])
+    bad = err > tol
+    msg = f"{what}: {int(bad.sum())} bad, max err {float(err.max()):.3e}"
+    assert bad.sum() <= stragglers * bad.size, msg
+    assert not (err > 2 * tol).any(), msg
 
 
 def _inputs(cfg):
@@ -254,6 +261,46 @@ def test_fwd_pipelined_kernel(ftk, g, D, N, qpad, kvpad, monkeypatch):
     ftk.check_errors()
     _close(o.float().cpu().numpy(), o2.float().cpu().numpy(), what="O pipelined vs exact")
     _close(lse.cpu().numpy(), lse2.cpu().numpy(), atol=1e-4, rtol=1e-5, what="lse vs exact")
+
+
+@pytest.mark.parametrize("g,kvb,D,dtype", [
+    (16, 16, 64, "fp16"),
+    (48, 48, 128, "fp16"),
+    (32, 32, 32, "bf16"),     # head dim padded to 64 by the host layer
+    (64, 64, 96, "bf16"),     # head dim padded to 128, pipelined forward
+    (64, 64, 128, "fp32"),    # fp32 in, computed in bf16, fp32 out
+    (32, 64, 128, "bf16"),    # four q-blocks per tile: exact forward kernel
+])
+def test_attention_block_shapes(ftk, g, kvb, D, dtype):
+    """Block sizes other than 64, head dims that need padding and fp32 inputs,
+    forward and backward against the oracle."""
+    H, N = 2, 384
+    cfg = dict(B=1, N=N, H=H, D=D, dtype="bf16" if dtype == "fp32" else dtype, seed=31, do_seed=32)
+    t = cases.make_inputs(cfg)
+    x = {k: v.float().numpy() for k, v in t.items()}
+    if dtype == "fp32":
+        t = {k: v.float() for k, v in t.items()}       # values already bf16-representable
+    QM, M = N // g, N // kvb
+    merged = _random_lists(np.random.default_rng(9), H, QM, M, 5, empty_every=7).reshape(1, H, QM, 5)
+    q = t["q"].cuda().requires_grad_(True)
+    k = t["k"].cuda().requires_grad_(True)
+    v = t["v"].cuda().requires_grad_(True)
+    o, lse = ftk.flash_topk_attn(q, k, v, torch.from_numpy(merged).cuda(), None, H, g, kvb)
+    ftk.check_errors()
+    assert o.dtype == q.dtype and o.shape == q.shape
+    wo, wl = orc.sparse_attn_fwd(x["q"], x["k"], x["v"], merged, H, g, kvb)
+    _close(o.detach().float().cpu().numpy(), wo, what="O")
+    _close(lse.cpu().numpy(), wl, what="lse")
+    o.backward(t["do"].cuda())
+    ftk.check_errors()
+    o_used = o.detach().float().cpu().numpy()
+    if dtype == "fp32":
+        o_used = torch.from_numpy(o_used).bfloat16().float().numpy()   # the kernels saw bf16 O
+    wq, wk, wv = orc.sparse_attn_bwd(x["q"], x["k"], x["v"], o_used, wl, x["do"], merged, H, g, kvb)
+    lax = 0.0 if dtype == "fp16" else 1e-4
+    _close(q.grad.float().cpu().numpy(), wq, what="dQ", stragglers=lax)
+    _close(k.grad.float().cpu().numpy(), wk, what="dK", stragglers=lax)
+    _close(v.grad.float().cpu().numpy(), wv, what="dV", stragglers=lax)
 
 
 def test_fwd_pipelined_redo_on_exponent_range(ftk, monkeypatch):
