@@ -551,11 +551,11 @@ extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int d
   e = encode_tmap_bnhd(&tv, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, kv_block_size);
   if (e) return e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // bf16, 64-row kv blocks, q-blocks of 64 or 128 rows and a workspace: the
+  // bf16, 64-row kv and q blocks and a workspace: the
   // pipelined kernel runs first and the exact kernel redoes the CTAs it flags.
   const char* env = getenv("FTK_FWD_PIPE");
   const bool pipe = dtype == FTK_DTYPE_BF16 && kv_block_size == 64 &&
-                    (q_block_size == 64 || q_block_size == 128) && workspace &&
+                    q_block_size == 64 && workspace &&
                     workspace_bytes >= ftk_sparse_fwd_workspace(B, H, QM, q_block_size) &&
                     !(env && env[0] == '0');
   if (pipe) {

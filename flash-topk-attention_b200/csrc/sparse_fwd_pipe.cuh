@@ -1,5 +1,5 @@
-// Deeply pipelined forward kernel for 64-row kv blocks, bf16, q-blocks of 64
-// or 128 rows.  Included by sparse_fwd.cu (shares FwdParams).
+// Deeply pipelined forward kernel for bf16 with 64-row kv blocks and 64-row
+// q-blocks.  Included by sparse_fwd.cu (shares FwdParams).
 //
 // The exact kernel keeps a running maximum per softmax group, which ties every
 // P tile to its group's accumulator: two groups, two O accumulators, two S
@@ -240,7 +240,7 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
     const int gw = (warp - 2) >> 2;          // softmax group = S buffer it drains
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
-    const int grp = r / p.g;                 // warp-uniform: q-blocks are 64 or 128 rows
+    const int grp = r / p.g;                 // warp-uniform: q-blocks are 64 rows
     const int qrow = tile_row0 + r;
     const bool row_valid = (grp < groups) && qrow >= 0 && qrow < p.N;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
