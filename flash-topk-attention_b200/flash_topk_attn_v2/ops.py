@@ -483,12 +483,47 @@ class FlashSparseAttnFunc(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None, None, None, None
 
 
+def _split_large_blocks(merged, N, g, kvb, q_pad_head, kv_pad_head):
+    """Lists over blocks of 65..128 rows, restated over half-size blocks.
+
+    The kernels work on q / kv blocks of at most 64 rows.  A block of `kvb` rows
+    that starts at token j*kvb - pad is exactly the two half blocks
+    2j - s, 2j - s + 1 of a grid with block kvb/2 and pad head pad - s*kvb/2,
+    where s = 1 when the pad head covers the first half block; each listed id
+    becomes those two ids (halves that lie before token 0 or at / after token N
+    are dropped).  q-blocks split the same way: both halves of a q-block take
+    its list.  Returns (merged', g', kvb', q_pad_head', kv_pad_head', M')."""
+    if kvb > 64:
+        half = kvb // 2
+        s = 1 if kv_pad_head >= half else 0
+        kv_pad_head -= s * half
+        sub0 = 2 * merged - s
+        sub = torch.stack([sub0, sub0 + 1], dim=-1)
+        start = sub.to(torch.int64) * half - kv_pad_head
+        keep = (merged >= 0).unsqueeze(-1) & (sub >= 0) & (start < N)
+        merged = torch.where(keep, sub, torch.full_like(sub, -1)).flatten(-2)
+        kvb = half
+    if g > 64:
+        half = g // 2
+        s = 1 if q_pad_head >= half else 0
+        q_pad_head -= s * half
+        qm2 = 2 * merged.shape[2] - s
+        parent = (torch.arange(qm2, device=merged.device) + s) // 2
+        merged = merged.index_select(2, parent)
+        g = half
+    m_kv = (kv_pad_head + N + kvb - 1) // kvb
+    return merged.contiguous(), g, kvb, q_pad_head, kv_pad_head, m_kv
+
+
 def flash_sparse_attn(q, k, v, merged_indices, num_heads, q_block_size, kv_block_size,
                       scale=None, q_padding=(0, 0), kv_padding=(0, 0)):
     """Block-sparse attention, differentiable in q, k, v: (O [B,N,C], lse [B,H,N]).
 
     Mirrors flash_sparse_attn (flash_topk_attn_v2/sparse_attn.py:227-392)
-    including its argument checks."""
+    including its argument checks, with one extension: q and kv blocks of up to
+    128 rows (multiples of 32 above 64) are accepted for forward and backward;
+    the reference rejects q blocks above 64 (sparse_attn.py:279) and its
+    dK/dV kernel is only correct up to 64-row kv blocks."""
     if q.ndim != 3:
         raise ValueError("q must be [B, N, C]")
     if q.device.type != "cuda":
@@ -503,10 +538,15 @@ def flash_sparse_attn(q, k, v, merged_indices, num_heads, q_block_size, kv_block
     D = C // H
     if C != H * D:
         raise ValueError(f"C ({C}) must be divisible by num_heads ({H})")
-    if q_block_size <= 0 or q_block_size > 64:
-        raise ValueError(f"q_block_size must be in (0, 64], got {q_block_size}")
+    if q_block_size <= 0 or q_block_size > 128:
+        raise ValueError(f"q_block_size must be in (0, 128], got {q_block_size}")
     if kv_block_size <= 0:
         raise ValueError(f"kv_block_size must be positive, got {kv_block_size}")
+    if kv_block_size > 128:
+        raise NotImplementedError(f"kv_block_size must be <= 128, got {kv_block_size}")
+    for name, blk in (("q_block_size", q_block_size), ("kv_block_size", kv_block_size)):
+        if blk > 64 and blk % 32 != 0:
+            raise NotImplementedError(f"{name} above 64 must be a multiple of 32, got {blk}")
     if merged_indices.ndim != 4:
         raise ValueError("merged_indices must be [B, H, QM, qblock_topk]")
     if merged_indices.dtype != torch.int32:
@@ -550,9 +590,14 @@ def flash_sparse_attn(q, k, v, merged_indices, num_heads, q_block_size, kv_block
         q = _pad_head_dim(q, False, H, D, Dk)
         k = _pad_head_dim(k, False, H, D, Dk)
         v = _pad_head_dim(v, False, H, D, Dk)
+    num_kv_blocks = n_kv // kv_block_size
+    if q_block_size > 64 or kv_block_size > 64:
+        (merged_indices, q_block_size, kv_block_size, q_pad_head, kv_pad_head,
+         num_kv_blocks) = _split_large_blocks(
+            merged_indices, N, q_block_size, kv_block_size, q_pad_head, kv_pad_head)
     o, lse = FlashSparseAttnFunc.apply(
         q, k, v, merged_indices, H, q_block_size, kv_block_size, scale, q_pad_head, kv_pad_head,
-        n_kv // kv_block_size)
+        num_kv_blocks)
     if Dk != D:
         o = o.view(B, N, H, Dk)[..., :D].reshape(B, N, C)
     if orig_dtype == torch.float32:

@@ -106,3 +106,43 @@ def test_no_fallback_when_library_missing(tmp_path, monkeypatch):
                         if p == _lib.LIB_PATH else _e(p))
     with pytest.raises(ImportError, match="no fallback"):
         _lib._load()
+
+
+def test_large_block_lists_split_into_half_blocks():
+    """q / kv blocks of 65..128 rows are restated over half-size blocks on the
+    host: every query row must keep exactly the same set of key tokens."""
+    import numpy as np
+    import torch
+    from flash_topk_attn_v2 import ops
+
+    def token_sets(merged, N, g, kvb, qph, kph):
+        qm = merged.shape[2]
+        out = []
+        for m in range(qm):
+            toks = set()
+            for j in merged[0, 0, m].tolist():
+                if j >= 0:
+                    toks.update(t for t in range(j * kvb - kph, (j + 1) * kvb - kph) if 0 <= t < N)
+            for r in range(m * g - qph, (m + 1) * g - qph):
+                if 0 <= r < N:
+                    out.append((r, frozenset(toks)))
+        return dict(out)
+
+    rng = np.random.default_rng(0)
+    for N, g, kvb, qpad, kpad in [(1000, 128, 128, (70, 82), (100, 52)),
+                                  (1000, 128, 64, (10, 14), (8, 16)),
+                                  (1000, 64, 128, (24, 0), (0, 24)),
+                                  (1000, 96, 96, (20, 36), (50, 6)),
+                                  (100, 128, 128, (14, 14), (27, 1))]:
+        QM, M = (qpad[0] + N + qpad[1]) // g, (kpad[0] + N + kpad[1]) // kvb
+        merged = np.full((1, 1, QM, 4), -1, dtype=np.int32)
+        for m in range(QM):
+            c = int(rng.integers(0, 5))
+            merged[0, 0, m, :c] = rng.permutation(M)[:c]
+        want = token_sets(merged, N, g, kvb, qpad[0], kpad[0])
+        m2, g2, kvb2, qph2, kph2, mkv2 = ops._split_large_blocks(
+            torch.from_numpy(merged), N, g, kvb, qpad[0], kpad[0])
+        assert g2 <= 64 and kvb2 <= 64 and 0 <= qph2 < g2 and 0 <= kph2 < kvb2
+        assert m2.shape[2] * g2 >= qph2 + N and int(m2.max()) < mkv2
+        got = token_sets(m2.numpy(), N, g2, kvb2, qph2, kph2)
+        assert got == want, (N, g, kvb)

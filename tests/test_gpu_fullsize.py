@@ -112,10 +112,11 @@ def test_config2_scoring(ftk):
     np.testing.assert_allclose(sc[0, 1, rows].cpu().numpy(), want, rtol=5e-6, atol=1e-10)
 
 
-def test_config4_ragged_score_select_merge(ftk):
+def test_config4_ragged_score_select_merge_attend(ftk):
     """B=2 N=30000 H=32 D=128 fp16, block 128, padding (40, 40), hot blocks,
-    threshold 0.8, merge at q_block_size 128 (reduced to 2 x 8 heads to keep
-    the host-side input generation short; shapes per slice are the config's)."""
+    threshold 0.8, merge at q_block_size 128, then attention forward and
+    backward at 128-row q / kv blocks (reduced to 2 x 8 heads to keep the
+    host-side input generation short; shapes per slice are the config's)."""
     cfg = dict(cases.BASELINE_CONFIGS[4], H=8)
     t = cases.make_inputs(cfg)
     H, D, b, K, thr = cfg["H"], cfg["D"], cfg["score_block_size"], cfg["topk"], cfg["threshold"]
@@ -141,6 +142,32 @@ def test_config4_ragged_score_select_merge(ftk):
     assert W == oW == g * K
     np.testing.assert_array_equal(merged.cpu().numpy(), om)
     np.testing.assert_array_equal(counts.cpu().numpy(), oc)
+
+    # attention at 128-row q and kv blocks over those lists (beyond the
+    # reference, which rejects q blocks above 64): forward and backward on the
+    # GPU, one (batch, head) slice re-done by the fp64 oracle
+    kvb = 128
+    qg = q.cuda().requires_grad_(True)
+    kg = k.cuda().requires_grad_(True)
+    vg = t["v"].cuda().requires_grad_(True)
+    o, lse = ftk.flash_topk_attn(qg, kg, vg, merged, counts, H, g, kvb,
+                                 kv_padding=pad, q_padding=qpad)
+    o.backward(t["do"].cuda())
+    ftk.check_errors()
+    assert torch.isfinite(o).all() and torch.isfinite(lse).all()
+    b_i, h_i = 1, 3
+    x = {n: _slice_head(t[n], b_i, h_i, D) for n in ("q", "k", "v", "do")}
+    m1 = om[b_i:b_i + 1, h_i:h_i + 1]
+    wo, wl = orc.sparse_attn_fwd(x["q"], x["k"], x["v"], m1, 1, g, kvb, None, qpad, pad)
+    go = o.detach()[b_i, :, h_i * D:(h_i + 1) * D].float().cpu().numpy()[None]
+    _close(go, wo, "O")
+    _close(lse[b_i, h_i].cpu().numpy(), wl[0, 0], "lse")
+    wq, wk, wv = orc.sparse_attn_bwd(x["q"], x["k"], x["v"], go, wl, x["do"], m1, 1, g, kvb,
+                                     None, qpad, pad)
+    sl = (b_i, slice(None), slice(h_i * D, (h_i + 1) * D))
+    _close(qg.grad[sl].float().cpu().numpy()[None], wq, "dQ")
+    _close(kg.grad[sl].float().cpu().numpy()[None], wk, "dK")
+    _close(vg.grad[sl].float().cpu().numpy()[None], wv, "dV")
 
 
 def test_config3_train_step_one_slice_exact(ftk):

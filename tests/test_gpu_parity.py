@@ -303,6 +303,41 @@ def test_attention_block_shapes(ftk, g, kvb, D, dtype):
     _close(v.grad.float().cpu().numpy(), wv, what="dV", stragglers=lax)
 
 
+@pytest.mark.parametrize("g,kvb,qpad,kvpad,dtype", [
+    (128, 128, (70, 82), (100, 52), "bf16"),
+    (128, 64, (10, 14), (8, 16), "fp16"),
+    (64, 128, (24, 0), (0, 24), "bf16"),
+    (96, 96, (20, 36), (50, 6), "fp16"),
+])
+def test_attention_blocks_up_to_128(ftk, g, kvb, qpad, kvpad, dtype):
+    """q / kv blocks above 64 rows (the reference rejects q blocks above 64 and
+    its dK/dV breaks for kv blocks above 64): forward and backward against the
+    oracle, with pad heads on either side of half a block."""
+    H, N, D = 2, 1000, 128
+    cfg = dict(B=1, N=N, H=H, D=D, dtype=dtype, seed=41, do_seed=42)
+    t = cases.make_inputs(cfg)
+    x = {k: v.float().numpy() for k, v in t.items()}
+    QM, M = (qpad[0] + N + qpad[1]) // g, (kvpad[0] + N + kvpad[1]) // kvb
+    merged = _random_lists(np.random.default_rng(13), H, QM, M, 4, empty_every=6).reshape(1, H, QM, 4)
+    q = t["q"].cuda().requires_grad_(True)
+    k = t["k"].cuda().requires_grad_(True)
+    v = t["v"].cuda().requires_grad_(True)
+    o, lse = ftk.flash_topk_attn(q, k, v, torch.from_numpy(merged).cuda(), None, H, g, kvb,
+                                 kv_padding=kvpad, q_padding=qpad)
+    ftk.check_errors()
+    wo, wl = orc.sparse_attn_fwd(x["q"], x["k"], x["v"], merged, H, g, kvb, None, qpad, kvpad)
+    _close(o.detach().float().cpu().numpy(), wo, what="O")
+    _close(lse.cpu().numpy(), wl, what="lse")
+    o.backward(t["do"].cuda())
+    ftk.check_errors()
+    wq, wk, wv = orc.sparse_attn_bwd(x["q"], x["k"], x["v"], o.detach().float().cpu().numpy(), wl,
+                                     x["do"], merged, H, g, kvb, None, qpad, kvpad)
+    lax = 0.0 if dtype == "fp16" else 1e-4
+    _close(q.grad.float().cpu().numpy(), wq, what="dQ", stragglers=lax)
+    _close(k.grad.float().cpu().numpy(), wk, what="dK", stragglers=lax)
+    _close(v.grad.float().cpu().numpy(), wv, what="dV", stragglers=lax)
+
+
 def test_fwd_pipelined_redo_on_exponent_range(ftk, monkeypatch):
     """Later blocks beat a row's first block by far more than 2^80: the
     pipelined kernel flags those tiles and the exact kernel redoes them, so
