@@ -101,7 +101,9 @@ def run_case(name: str, ref) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True,
+                    help="checkout of YouHuang67/flash-topk-attention (its pure-PyTorch "
+                         "_naive functions are imported from it and run on the CPU)")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     torch.manual_seed(0)
