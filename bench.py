@@ -51,6 +51,29 @@ def measured_peaks():
 
 
 # ---------------------------------------------------------------------------
+# host placement
+# ---------------------------------------------------------------------------
+def bind_near_gpu(index):
+    """Run this rank on the CPU cores next to its GPU (read from NVML), so the
+    pinned host buffers it allocates afterwards land on that NUMA node and the
+    end-to-end copies do not cross sockets.  Only the process's own CPU affinity
+    changes; nothing about the GPU is set.  Returns the number of cores or None."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return len(cpus)
+    except Exception:
+        return None
+
+
+# ---------------------------------------------------------------------------
 # synthetic inputs
 # ---------------------------------------------------------------------------
 def make_host_inputs(cfg, seed):
@@ -131,6 +154,7 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    near = bind_near_gpu(local) if world > 1 else None
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
@@ -302,6 +326,7 @@ def run_ours(args):
             "config": {"workload": cfg["name"], "B_per_gpu": B, "N": N, "H": H, "D": D,
                        "score_block_size": b, "topk": K, "threshold": thr, "q_block_size": g,
                        "kv_block_size": kvb, "sharding": "batch x head slices, no collective",
+                       "host_cores_near_gpu": near,
                        "l2": "inputs larger than L2 (4 x 268 MB per step)",
                        "candidate_pairs_per_step": P},
             "clocks": clocks,
