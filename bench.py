@@ -176,7 +176,7 @@ def run_ours(args):
     stage_ms = {"score_select": 0.0, "merge": 0.0, "sparse_fwd": 0.0, "sparse_bwd": 0.0}
     pairs = [0]
 
-    def step(record):
+    def step(record, before_attn=None, after_fwd=None):
         evs = [torch.cuda.Event(enable_timing=True) for _ in range(5)] if record else None
         q = devt["q"].detach().requires_grad_(True)
         k = devt["k"].detach().requires_grad_(True)
@@ -189,9 +189,13 @@ def run_ours(args):
         merged, counts, W = ftk.build_qblock_topk_indices(idx, g, topk_scores=avg)
         if record:
             evs[2].record()
+        if before_attn is not None:
+            before_attn()          # end-to-end leg: V and dO have arrived
         o, lse = ftk.flash_topk_attn(q, k, v, merged, counts, H, g, kvb)
         if record:
             evs[3].record()
+        if after_fwd is not None:
+            after_fwd(o)           # end-to-end leg: O goes home under the backward
         o.backward(devt["do"])
         if record:
             evs[4].record()
@@ -238,18 +242,32 @@ def run_ours(args):
     # results go back to pinned host memory, all inside the timed region.  The
     # copies run on two side streams (PCIe is full duplex) over double-buffered
     # device inputs, so step i+1's upload and step i-1's download overlap step
-    # i's kernels; dependencies are CUDA events only.
+    # i's kernels; scoring starts as soon as Q and K are there (V and dO follow
+    # under it) and O leaves under the backward.  Dependencies are CUDA events.
     cur = torch.cuda.current_stream(dev)
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     bufs = [devt, {k: torch.empty_like(v) for k, v in devt.items()}]
+    ev_qk = [torch.cuda.Event(), torch.cuda.Event()]
     ev_in = [torch.cuda.Event(), torch.cuda.Event()]
     ev_done = [torch.cuda.Event(), torch.cuda.Event()]
 
     def upload(i):
         with torch.cuda.stream(s_in):
-            for k in host:
+            for k in ("q", "k"):
+                bufs[i % 2][k].copy_(host[k], non_blocking=True)
+            ev_qk[i % 2].record(s_in)
+            for k in ("v", "do"):
                 bufs[i % 2][k].copy_(host[k], non_blocking=True)
             ev_in[i % 2].record(s_in)
+
+    def download(names, tensors):
+        ev = torch.cuda.Event()
+        ev.record(cur)
+        s_out.wait_event(ev)
+        with torch.cuda.stream(s_out):
+            for nm, t in zip(names, tensors):
+                host_out[nm].copy_(t, non_blocking=True)
+                t.record_stream(s_out)
 
     barrier()
     e0 = torch.cuda.Event(enable_timing=True)
@@ -261,8 +279,9 @@ def run_ours(args):
     keep = []
     for i in range(args.steps):
         devt = bufs[i % 2]
-        cur.wait_event(ev_in[i % 2])
-        _, res = step(False)
+        cur.wait_event(ev_qk[i % 2])
+        _, res = step(False, before_attn=lambda i=i: cur.wait_event(ev_in[i % 2]),
+                      after_fwd=lambda o: download(("o",), (o.detach(),)))
         ev_done[i % 2].record(cur)
         if i + 1 < args.steps:
             if i >= 1:
@@ -270,11 +289,7 @@ def run_ours(args):
                 # must not overwrite it before that step's kernels finished
                 s_in.wait_event(ev_done[(i + 1) % 2])
             upload(i + 1)
-        s_out.wait_event(ev_done[i % 2])
-        with torch.cuda.stream(s_out):
-            for nm, t in zip(("o", "dq", "dk", "dv"), res[:4]):
-                host_out[nm].copy_(t, non_blocking=True)
-                t.record_stream(s_out)
+        download(("dq", "dk", "dv"), res[1:4])
         keep.append(res)
     cur.wait_stream(s_out)
     cur.wait_stream(s_in)
