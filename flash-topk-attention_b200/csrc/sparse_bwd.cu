@@ -18,6 +18,7 @@
 //        128 kv rows, so dK/dV need no atomics.
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 
 #include "attn_common.cuh"
 #include "ftk_host.cuh"
@@ -760,6 +761,12 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
+}  // namespace ftk
+
+#include "sparse_bwd_dkv2.cuh"
+
+namespace ftk {
+
 static int bwd_common_checks(int dtype, int64_t B, int64_t H, int64_t N, int64_t D, int QM, int g,
                              int kvb, int q_pad_head, int kv_pad_head) {
   if (B <= 0 || H <= 0 || N <= 0 || QM <= 0) return FTK_ERR_BAD_ARG;
@@ -915,6 +922,21 @@ extern "C" int ftk_sparse_bwd_dkv(
     return e;
   if ((e = encode_tmap_bnhd(&tk, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, 128))) return e;
   if ((e = encode_tmap_bnhd(&tv, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, 128))) return e;
+  // head dim 128 with 64-row q and kv blocks: the kernel on pairs of SMs
+  const char* env2 = getenv("FTK_DKV_2CTA");
+  if (D == 128 && q_block_size == 64 && kv_block_size == 64 && !(env2 && env2[0] == '0')) {
+    CUtensorMap tq32, tdo32;
+    if ((e = encode_tmap_bnhd(&tq32, q, dtype, B, N, H, D, sq_b, sq_n, sq_h, 64, 32))) return e;
+    if ((e = encode_tmap_bnhd(&tdo32, dout, dtype, B, N, H, D, sdo_b, sdo_n, sdo_h, 64, 32)))
+      return e;
+    const size_t smem2 = 1024 + 2 * 2 * 128 * 128 + static_cast<size_t>(DK2_STAGES) * 32768;
+    if (cudaFuncSetAttribute(sparse_bwd_dkv2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem2)) != cudaSuccess)
+      return FTK_ERR_CUDA;
+    dim3 grid2(2 * ((M + 3) / 4), static_cast<unsigned>(B * H));
+    sparse_bwd_dkv2_kernel<<<grid2, BW_THREADS, smem2, st>>>(tq, tdo, tq32, tdo32, tk, tv, p);
+    return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+  }
   const int nch = static_cast<int>(D / 64);
   const int stage_bytes = 2 * nch * q_block_size * 128;
   p.nstages = std::min(BW_MAX_STAGES, (128 * 1024) / stage_bytes);
