@@ -50,6 +50,32 @@ __global__ void delta_kernel(const uint8_t* __restrict__ o, const uint8_t* __res
   if (lane == 0) delta[(b * H + h) * N + n] = acc;
 }
 
+// dS = 2^(c s - lse2) (dp - delta) for 32 columns of one row, two columns per
+// instruction (fma.f32x2, add.f32x2, mul.f32x2, one cvt per pair).
+template <int FMT>
+__device__ __forceinline__ void ds_pairs(const uint32_t (&sv)[32], const uint32_t (&dv)[32],
+                                         uint32_t (&pk)[16], float c, float neg_lse2,
+                                         float neg_delta) {
+  const float2 c2 = make_float2(c, c), nl = make_float2(neg_lse2, neg_lse2),
+               nd = make_float2(neg_delta, neg_delta);
+#pragma unroll
+  for (int x = 0; x < 32; x += 2) {
+    const float2 t =
+        __ffma2_rn(make_float2(__uint_as_float(sv[x]), __uint_as_float(sv[x + 1])), c2, nl);
+    const float2 pr = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+    const float2 dd =
+        __fadd2_rn(make_float2(__uint_as_float(dv[x]), __uint_as_float(dv[x + 1])), nd);
+    const float2 ds = __fmul2_rn(pr, dd);
+    if (FMT == 1) {
+      __nv_bfloat162 v = __floats2bfloat162_rn(ds.x, ds.y);
+      pk[x >> 1] = *reinterpret_cast<uint32_t*>(&v);
+    } else {
+      __half2 v = __floats2half2_rn(ds.x, ds.y);
+      pk[x >> 1] = *reinterpret_cast<uint32_t*>(&v);
+    }
+  }
+}
+
 constexpr int BW_THREADS = 576;  // 2 + 2 x 8 warps
 constexpr int BW_MAX_STAGES = 4;
 constexpr int DQ_KST = 7;        // dQ kernel: K tiles in the ring (held until dQ += dS K ran)
@@ -346,13 +372,8 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
           tmem_ld32(dp_addr + c0, dv);
           tmem_wait_ld();
           if (fast) {
-#pragma unroll
-            for (int x = 0; x < 32; x += 2) {
-              const float p0 = fast_exp2(fmaf(__uint_as_float(sv[x]), c, -lse2));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(sv[x + 1]), c, -lse2));
-              pk[x >> 1] = pack2(p0 * (__uint_as_float(dv[x]) - dl),
-                                 p1 * (__uint_as_float(dv[x + 1]) - dl), p.fmt);
-            }
+            if (p.fmt == 1) ds_pairs<1>(sv, dv, pk, c, -lse2, -dl);
+            else ds_pairs<0>(sv, dv, pk, c, -lse2, -dl);
           } else {
 #pragma unroll
             for (int x = 0; x < 32; x += 2) {
@@ -930,11 +951,20 @@ extern "C" int ftk_sparse_bwd_dkv(
     if ((e = encode_tmap_bnhd(&tdo32, dout, dtype, B, N, H, D, sdo_b, sdo_n, sdo_h, 64, 32)))
       return e;
     const size_t smem2 = 1024 + 2 * 2 * 128 * 128 + static_cast<size_t>(DK2_STAGES) * 32768;
-    if (cudaFuncSetAttribute(sparse_bwd_dkv2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem2)) != cudaSuccess)
-      return FTK_ERR_CUDA;
     dim3 grid2(2 * ((M + 3) / 4), static_cast<unsigned>(B * H));
-    sparse_bwd_dkv2_kernel<<<grid2, BW_THREADS, smem2, st>>>(tq, tdo, tq32, tdo32, tk, tv, p);
+    if (dtype == FTK_DTYPE_BF16) {
+      if (cudaFuncSetAttribute(sparse_bwd_dkv2_kernel<1>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem2)) != cudaSuccess)
+        return FTK_ERR_CUDA;
+      sparse_bwd_dkv2_kernel<1><<<grid2, BW_THREADS, smem2, st>>>(tq, tdo, tq32, tdo32, tk, tv, p);
+    } else {
+      if (cudaFuncSetAttribute(sparse_bwd_dkv2_kernel<0>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem2)) != cudaSuccess)
+        return FTK_ERR_CUDA;
+      sparse_bwd_dkv2_kernel<0><<<grid2, BW_THREADS, smem2, st>>>(tq, tdo, tq32, tdo32, tk, tv, p);
+    }
     return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
   }
   const int nch = static_cast<int>(D / 64);

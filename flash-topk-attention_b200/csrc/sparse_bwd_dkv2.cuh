@@ -88,6 +88,17 @@ __device__ __forceinline__ void umma2_commit(uint32_t bar, uint16_t cta_mask) {
 // first half), dP^T[2] 128/192 (dS^T likewise), dV 256.., dK 384..
 // Shared memory per CTA: K 32 KB, V 32 KB, 4 stages of
 //   [Q rows-half 8 KB][dO rows-half 8 KB][Q d-half 8 KB][dO d-half 8 KB].
+template <int FMT>
+__device__ __forceinline__ uint32_t pack2f(float a, float b) {
+  if (FMT == 1) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int FMT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(BW_THREADS, 1)
 sparse_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q,
                        const __grid_constant__ CUtensorMap tm_do,
@@ -208,8 +219,8 @@ sparse_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q,
   } else if (warp == 1) {
     // ----------------------------- CTA 0: UMMA issuer for the CTA pair
     if (n > 0) {
-      const uint32_t idesc_a = umma_idesc(256, G, p.fmt, 0, 0);
-      const uint32_t idesc_b = umma_idesc(256, D, p.fmt, 0, 1);
+      const uint32_t idesc_a = umma_idesc(256, G, FMT, 0, 0);
+      const uint32_t idesc_b = umma_idesc(256, D, FMT, 0, 1);
       const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sK), 16, 1024);
       const uint64_t vdesc0 = smem_desc_sw128(smem_u32(sV), 16, 1024);
       const uint64_t rowdesc0 = smem_desc_sw128(smem_u32(sQD), 16, 1024);
@@ -300,23 +311,35 @@ sparse_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q,
     const int cbeg = colhalf * 32;
     const float c = p.scale_log2;
     bool ok = true;
+    // lse / delta of a q-block are fetched from global memory one round ahead
+    // (into registers, while the previous tile is being worked on) and only
+    // then staged in shared memory: their latency stays out of the per-tile
+    // chain  S^T, dP^T ready -> P^T, dS^T -> dV, dK.
+    auto fetch = [&](int i, float& l2, float& dl) {
+      l2 = 0.f;
+      dl = 0.f;
+      if (ct < G && i < n) {
+        const int t = static_cast<int>(un.ids[i]) * G - p.q_pad_head + ct;
+        if (t >= 0 && t < p.N) {   // stored negated: the packed fma / add take them as they are
+          l2 = -p.lse[static_cast<int64_t>(bh) * p.N + t] * 1.4426950408889634f;
+          dl = -p.delta[static_cast<int64_t>(bh) * p.N + t];
+        }
+      }
+    };
+    float l2_next, dl_next;
+    fetch(wg, l2_next, dl_next);
     for (int i = wg; i < n; i += 2) {
       const int pb = (i >> 1) & 1;           // per-group double buffer of lse / delta
       const int row0 = static_cast<int>(un.ids[i]) * G - p.q_pad_head;
       if (ct < G) {
-        const int t = row0 + ct;
-        float l2 = 0.f, dl = 0.f;
-        if (t >= 0 && t < p.N) {
-          l2 = p.lse[static_cast<int64_t>(bh) * p.N + t] * 1.4426950408889634f;
-          dl = p.delta[static_cast<int64_t>(bh) * p.N + t];
-        }
-        s_lse2[wg][pb][ct] = l2;
-        s_delta[wg][pb][ct] = dl;
+        s_lse2[wg][pb][ct] = l2_next;
+        s_delta[wg][pb][ct] = dl_next;
       }
       if (wg == 0)
         asm volatile("bar.sync 1, 256;" ::: "memory");
       else
         asm volatile("bar.sync 2, 256;" ::: "memory");
+      fetch(i + 2, l2_next, dl_next);
       if (!ok) continue;
       if (!mbar_wait(bar_afull(wg), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) {
         ok = false;
@@ -328,33 +351,70 @@ sparse_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q,
       const bool fast = __all_sync(0xffffffffu, act) && lo == 0 && hi == G;
       const float4* l4 = reinterpret_cast<const float4*>(s_lse2[wg][pb]);
       const float4* d4 = reinterpret_cast<const float4*>(s_delta[wg][pb]);
-      for (int c0 = cbeg; c0 < cbeg + 32; c0 += 16) {
-        uint32_t sv[16], dv[16], pp[8], pd[8];
-        tmem_ld16(st_addr + c0, sv);
-        tmem_ld16(dp_addr + c0, dv);
-        tmem_wait_ld();
+      // The thread's 32 columns in two chunks of 16; the loads of the second
+      // chunk are in flight while the first is worked on.  P^T / dS^T of
+      // columns [c0, c0+16) go over columns cbeg + (c0-cbeg)/2 .. of the S^T /
+      // dP^T regions: columns this thread has already read.
+      // full tiles: two columns per instruction (fma.f32x2, add.f32x2,
+      // mul.f32x2, one cvt per pair); lse / delta come negated from shared
+      // memory as one 16-byte broadcast load per four columns
+      auto work = [&](const uint32_t (&sv)[16], const uint32_t (&dv)[16], int c0) {
+        uint32_t pp[8], pd[8];
+        const float2 c2 = make_float2(c, c);
+        if (fast) {
 #pragma unroll
-        for (int x = 0; x < 16; x += 4) {
-          const float4 lq = l4[(c0 + x) >> 2];
-          const float4 dq = d4[(c0 + x) >> 2];
-          const float ls[4] = {lq.x, lq.y, lq.z, lq.w};
-          const float ds[4] = {dq.x, dq.y, dq.z, dq.w};
-          float pv[4], dsv[4];
+          for (int x = 0; x < 16; x += 4) {
+            const float4 lq = l4[(c0 + x) >> 2];
+            const float4 dq = d4[(c0 + x) >> 2];
 #pragma unroll
-          for (int y = 0; y < 4; y++) {
-            const bool on = fast || (act && c0 + x + y >= lo && c0 + x + y < hi);
-            const float pr = on ? fast_exp2(fmaf(__uint_as_float(sv[x + y]), c, -ls[y])) : 0.f;
-            pv[y] = pr;
-            dsv[y] = pr * (__uint_as_float(dv[x + y]) - ds[y]);
+            for (int y = 0; y < 4; y += 2) {
+              const float2 nl = y == 0 ? make_float2(lq.x, lq.y) : make_float2(lq.z, lq.w);
+              const float2 nd = y == 0 ? make_float2(dq.x, dq.y) : make_float2(dq.z, dq.w);
+              const float2 t = __ffma2_rn(
+                  make_float2(__uint_as_float(sv[x + y]), __uint_as_float(sv[x + y + 1])), c2, nl);
+              const float2 pr = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+              const float2 dd = __fadd2_rn(
+                  make_float2(__uint_as_float(dv[x + y]), __uint_as_float(dv[x + y + 1])), nd);
+              const float2 dsv = __fmul2_rn(pr, dd);
+              pp[(x + y) >> 1] = pack2f<FMT>(pr.x, pr.y);
+              pd[(x + y) >> 1] = pack2f<FMT>(dsv.x, dsv.y);
+            }
           }
-          pp[x >> 1] = pack2(pv[0], pv[1], p.fmt);
-          pp[(x >> 1) + 1] = pack2(pv[2], pv[3], p.fmt);
-          pd[x >> 1] = pack2(dsv[0], dsv[1], p.fmt);
-          pd[(x >> 1) + 1] = pack2(dsv[2], dsv[3], p.fmt);
+        } else {
+#pragma unroll
+          for (int x = 0; x < 16; x += 4) {
+            const float4 lq = l4[(c0 + x) >> 2];
+            const float4 dq = d4[(c0 + x) >> 2];
+            const float ls[4] = {lq.x, lq.y, lq.z, lq.w};
+            const float ds[4] = {dq.x, dq.y, dq.z, dq.w};
+            float pv[4], dsv[4];
+#pragma unroll
+            for (int y = 0; y < 4; y++) {
+              const bool on = act && c0 + x + y >= lo && c0 + x + y < hi;
+              const float pr = on ? fast_exp2(fmaf(__uint_as_float(sv[x + y]), c, ls[y])) : 0.f;
+              pv[y] = pr;
+              dsv[y] = pr * (__uint_as_float(dv[x + y]) + ds[y]);
+            }
+            pp[x >> 1] = pack2f<FMT>(pv[0], pv[1]);
+            pp[(x >> 1) + 1] = pack2f<FMT>(pv[2], pv[3]);
+            pd[x >> 1] = pack2f<FMT>(dsv[0], dsv[1]);
+            pd[(x >> 1) + 1] = pack2f<FMT>(dsv[2], dsv[3]);
+          }
         }
         const int oc = cbeg + ((c0 - cbeg) >> 1);
         tmem_st8(st_addr + oc, pp);
         tmem_st8(dp_addr + oc, pd);
+      };
+      {
+        uint32_t sa[16], da[16], sb2[16], db2[16];
+        tmem_ld16(st_addr + cbeg, sa);
+        tmem_ld16(dp_addr + cbeg, da);
+        tmem_wait_ld();
+        tmem_ld16(st_addr + cbeg + 16, sb2);
+        tmem_ld16(dp_addr + cbeg + 16, db2);
+        work(sa, da, cbeg);
+        tmem_wait_ld();
+        work(sb2, db2, cbeg + 16);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -386,7 +446,7 @@ sparse_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q,
           for (int x = 0; x < 32; x += 2) {
             const float a = n > 0 ? __uint_as_float(v[x]) * mul : 0.f;
             const float b = n > 0 ? __uint_as_float(v[x + 1]) * mul : 0.f;
-            pk[x >> 1] = pack2(a, b, p.fmt);
+            pk[x >> 1] = pack2f<FMT>(a, b);
           }
           uint4* dst = reinterpret_cast<uint4*>(orow + c0 * 2);
 #pragma unroll
