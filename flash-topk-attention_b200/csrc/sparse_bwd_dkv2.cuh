@@ -18,7 +18,9 @@
 // UMMA; tcgen05.commit multicasts its arrivals to both CTAs' barriers; the
 // other CTA's warp 1 forwards "my tiles have landed" to CTA 0 and its compute
 // warps arrive on CTA 0's barriers through the cluster shared-memory window.
-// No TMA load is multicast.
+// No TMA load is multicast.  With the UMMAs this cheap the compute warps set
+// the pace: they use two-column instructions (fma / add / mul .f32x2), fetch
+// lse / delta a round ahead, and all 16 of them work on every tile.
 #pragma once
 
 namespace ftk {
@@ -153,7 +155,7 @@ sparse_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
     for (int s = 0; s < 2; s++) {
       mbar_init(bar_afull(s), 1);
-      mbar_init(bar_pfull(s), 16);   // 8 warps of the owning group in each CTA
+      mbar_init(bar_pfull(s), 32);   // the 16 compute warps of each CTA
     }
     mbar_init(bar_final, 1);
     mbar_init_fence();
@@ -263,7 +265,7 @@ sparse_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
         for (int ks = 0; ks < 4; ks++) {
           const bool acc = (i > 0) || (ks > 0);
-          const uint32_t col = sb * 64 + (ks >> 1) * 32 + (ks & 1) * 8;
+          const uint32_t col = sb * 64 + ks * 16;   // written by the warps of column quarter ks
           umma2_ts(tmem + 256, tmem + col, desc_advance(docol, ks * 2048), idesc_b, acc);
           umma2_ts(tmem + 384, tmem + 128 + col, desc_advance(qcol, ks * 2048), idesc_b, acc);
         }
@@ -293,28 +295,27 @@ sparse_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q,
       __syncwarp();
     }
   } else if (warp >= 2) {
-    // Two groups of 8 warps per CTA; group w drains the buffers of tiles
-    // i = w (mod 2); two warps share each 32-row lane quarter and take one half
-    // of the q columns each.
+    // All 16 compute warps of a CTA work on every tile: four warps share each
+    // 32-row lane quarter and take 16 of the 64 q columns each.  A tile's
+    // exponentials then take half as long as with one 8-warp group per
+    // buffer, and that time is part of the per-buffer chain
+    //   S^T, dP^T ready -> P^T, dS^T -> dV, dK -> next S^T, dP^T
+    // that bounds the kernel; the two buffers still overlap each other.
     const int cw = warp - 2;
-    const int wg = cw >> 3;
-    const int colhalf = (cw >> 2) & 1;
+    const int colq = cw >> 2;
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
-    const int ct = (tid - 64) & 255;         // index inside the group
+    const int ct = tid - 64;                 // index among the compute threads
     const int grp = 2 * static_cast<int>(rank) + r / G;   // kv block of the pair
     const int tok = tile_tok0 + r;
     const bool row_valid = (grp < groups) && tok >= 0 && tok < p.N;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t st_addr = lane_addr + wg * 64;         // S^T, then P^T
-    const uint32_t dp_addr = lane_addr + 128 + wg * 64;   // dP^T, then dS^T
-    const int cbeg = colhalf * 32;
+    const int cbeg = colq * 16;
     const float c = p.scale_log2;
     bool ok = true;
     // lse / delta of a q-block are fetched from global memory one round ahead
     // (into registers, while the previous tile is being worked on) and only
-    // then staged in shared memory: their latency stays out of the per-tile
-    // chain  S^T, dP^T ready -> P^T, dS^T -> dV, dK.
+    // then staged in shared memory: their latency stays out of the chain.
     auto fetch = [&](int i, float& l2, float& dl) {
       l2 = 0.f;
       dl = 0.f;
@@ -327,34 +328,31 @@ sparse_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
     };
     float l2_next, dl_next;
-    fetch(wg, l2_next, dl_next);
-    for (int i = wg; i < n; i += 2) {
-      const int pb = (i >> 1) & 1;           // per-group double buffer of lse / delta
+    fetch(0, l2_next, dl_next);
+    for (int i = 0; i < n; i++) {
+      const int sb = i & 1;                  // S^T / dP^T buffer, and lse / delta buffer
       const int row0 = static_cast<int>(un.ids[i]) * G - p.q_pad_head;
       if (ct < G) {
-        s_lse2[wg][pb][ct] = l2_next;
-        s_delta[wg][pb][ct] = dl_next;
+        s_lse2[0][sb][ct] = l2_next;
+        s_delta[0][sb][ct] = dl_next;
       }
-      if (wg == 0)
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-      else
-        asm volatile("bar.sync 2, 256;" ::: "memory");
-      fetch(i + 2, l2_next, dl_next);
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      fetch(i + 1, l2_next, dl_next);
       if (!ok) continue;
-      if (!mbar_wait(bar_afull(wg), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) {
+      if (!mbar_wait(bar_afull(sb), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) {
         ok = false;
         continue;
       }
       tc_fence_after();
+      const uint32_t st_addr = lane_addr + sb * 64;         // S^T, then P^T
+      const uint32_t dp_addr = lane_addr + 128 + sb * 64;   // dP^T, then dS^T
       const int lo = max(0, -row0), hi = min(G, p.N - row0);
       const bool act = row_valid && ((un.masks[i] >> grp) & 1) && hi > lo;
       const bool fast = __all_sync(0xffffffffu, act) && lo == 0 && hi == G;
-      const float4* l4 = reinterpret_cast<const float4*>(s_lse2[wg][pb]);
-      const float4* d4 = reinterpret_cast<const float4*>(s_delta[wg][pb]);
-      // The thread's 32 columns in two chunks of 16; the loads of the second
-      // chunk are in flight while the first is worked on.  P^T / dS^T of
-      // columns [c0, c0+16) go over columns cbeg + (c0-cbeg)/2 .. of the S^T /
-      // dP^T regions: columns this thread has already read.
+      const float4* l4 = reinterpret_cast<const float4*>(s_lse2[0][sb]);
+      const float4* d4 = reinterpret_cast<const float4*>(s_delta[0][sb]);
+      // P^T / dS^T of the thread's 16 columns go over the first 8 of them in
+      // the S^T / dP^T regions: columns this thread has already read.
       // full tiles: two columns per instruction (fma.f32x2, add.f32x2,
       // mul.f32x2, one cvt per pair); lse / delta come negated from shared
       // memory as one 16-byte broadcast load per four columns
@@ -401,31 +399,26 @@ sparse_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q,
             pd[(x >> 1) + 1] = pack2f<FMT>(dsv[2], dsv[3]);
           }
         }
-        const int oc = cbeg + ((c0 - cbeg) >> 1);
-        tmem_st8(st_addr + oc, pp);
-        tmem_st8(dp_addr + oc, pd);
+        tmem_st8(st_addr + c0, pp);
+        tmem_st8(dp_addr + c0, pd);
       };
       {
-        uint32_t sa[16], da[16], sb2[16], db2[16];
+        uint32_t sa[16], da[16];
         tmem_ld16(st_addr + cbeg, sa);
         tmem_ld16(dp_addr + cbeg, da);
         tmem_wait_ld();
-        tmem_ld16(st_addr + cbeg + 16, sb2);
-        tmem_ld16(dp_addr + cbeg + 16, db2);
         work(sa, da, cbeg);
-        tmem_wait_ld();
-        work(sb2, db2, cbeg + 16);
       }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cta(bar_pfull(wg), 0);
+      if (lane == 0) mbar_arrive_cta(bar_pfull(sb), 0);
     }
     if (ok && n > 0) ok = mbar_wait(bar_final, 0, w, FTK_DEV_TIMEOUT_EPILOGUE);
     if (ok) {
       tc_fence_after();
-      // group 0 stores dV (TMEM 256..), group 1 stores dK (TMEM 384.., scaled)
-      const int which = wg;
+      // column quarters 0, 1 store dV (TMEM 256..), 2, 3 store dK (TMEM 384.., scaled)
+      const int which = colq >> 1, colhalf = colq & 1;
       uint8_t* base = static_cast<uint8_t*>(which == 0 ? p.out1 : p.out0);
       const int64_t sb_ = which == 0 ? p.s1_b : p.s0_b, sn_ = which == 0 ? p.s1_n : p.s0_n,
                     sh_ = which == 0 ? p.s1_h : p.s0_h;
