@@ -785,6 +785,7 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
 }  // namespace ftk
 
 #include "sparse_bwd_dkv2.cuh"
+#include "sparse_bwd_dq2.cuh"
 
 namespace ftk {
 
@@ -866,6 +867,29 @@ extern "C" int ftk_sparse_bwd_dq(
     return e;
   if ((e = encode_tmap_bnhd(&tv, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, kv_block_size)))
     return e;
+  // head dim 128 with 64-row q and kv blocks: the kernel on pairs of SMs
+  const char* env2 = getenv("FTK_DQ_2CTA");
+  if (D == 128 && q_block_size == 64 && kv_block_size == 64 && !(env2 && env2[0] == '0')) {
+    CUtensorMap tk32, tv32;
+    if ((e = encode_tmap_bnhd(&tk32, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, 32))) return e;
+    if ((e = encode_tmap_bnhd(&tv32, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, 32))) return e;
+    const size_t smem2 = 1024 + 2 * 2 * 128 * 128 + static_cast<size_t>(DQ2_STAGES) * 24576;
+    dim3 grid2(2 * ((QM + 3) / 4), static_cast<unsigned>(B * H));
+    if (dtype == FTK_DTYPE_BF16) {
+      if (cudaFuncSetAttribute(sparse_bwd_dq2_kernel<1>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem2)) != cudaSuccess)
+        return FTK_ERR_CUDA;
+      sparse_bwd_dq2_kernel<1><<<grid2, BW_THREADS, smem2, st>>>(tq, tdo, tk, tk32, tv32, p);
+    } else {
+      if (cudaFuncSetAttribute(sparse_bwd_dq2_kernel<0>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem2)) != cudaSuccess)
+        return FTK_ERR_CUDA;
+      sparse_bwd_dq2_kernel<0><<<grid2, BW_THREADS, smem2, st>>>(tq, tdo, tk, tk32, tv32, p);
+    }
+    return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+  }
   const int nch = static_cast<int>(D / 64);
   // four V slots lie over the Q / dO tiles, the rest of the V ring behind the K ring
   const size_t smem = 1024 + 2 * nch * 128 * 128 +
