@@ -452,6 +452,7 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 }  // namespace ftk
 
 #include "sparse_fwd_pipe.cuh"
+#include "sparse_fwd_pipe2.cuh"
 
 namespace ftk {
 
@@ -560,8 +561,23 @@ extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int d
                     !(env && env[0] == '0');
   if (pipe) {
     p.redo_out = static_cast<int*>(workspace);
-    e = (D == 64) ? launch_fwd_pipe<64>(tq, tk, tv, p, B * H, st)
-                  : launch_fwd_pipe<128>(tq, tk, tv, p, B * H, st);
+    const char* env2 = getenv("FTK_FWD_2CTA");
+    if (D == 128 && !(env2 && env2[0] == '0')) {
+      // head dim 128: the same kernel on pairs of SMs
+      CUtensorMap tk32;
+      e = encode_tmap_bnhd(&tk32, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, 32);
+      if (e) return e;
+      const size_t smem2 = 1024 + 2 * 128 * 128 + static_cast<size_t>(FP2_KST + FP2_VST) * 8192;
+      if (cudaFuncSetAttribute(sparse_fwd_pipe2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem2)) != cudaSuccess)
+        return FTK_ERR_CUDA;
+      dim3 grid2(2 * ((QM + 3) / 4), static_cast<unsigned>(B * H));
+      sparse_fwd_pipe2_kernel<<<grid2, FP_THREADS, smem2, st>>>(tq, tk32, tv, p);
+      e = cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+    } else {
+      e = (D == 64) ? launch_fwd_pipe<64>(tq, tk, tv, p, B * H, st)
+                    : launch_fwd_pipe<128>(tq, tk, tv, p, B * H, st);
+    }
     if (e) return e;
     p.redo_out = nullptr;
     p.redo_in = static_cast<const int*>(workspace);
