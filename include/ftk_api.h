@@ -186,7 +186,8 @@ int ftk_sort_by_count(const int32_t* counts, int64_t total, int max_count,
  * kernel, launched behind it, recomputes the tiles whose scores left the safe
  * exponent range (none on ordinary inputs).  Without a workspace only the
  * exact kernel runs.  Setting the environment variable FTK_FWD_PIPE=0 does the
- * same. */
+ * same.  At head dim 128 the pipelined kernel runs on pairs of SMs (clusters of
+ * two CTAs, tcgen05 cta_group::2); FTK_FWD_2CTA=0 selects the one-CTA form. */
 size_t ftk_sparse_fwd_workspace(int64_t B, int64_t H, int QM, int q_block_size);
 int ftk_sparse_fwd(const void* q, const void* k, const void* v, int dtype, int64_t B, int64_t H,
                    int64_t N, int64_t D, int64_t sq_b, int64_t sq_n, int64_t sq_h, int64_t sk_b,
@@ -200,6 +201,9 @@ int ftk_sparse_fwd(const void* q, const void* k, const void* v, int dtype, int64
  * sparse_attn_bwd_dq_launch (csrc/sparse_attn_bwd_dq.cpp:3-15,
  * csrc/sparse_attn_bwd_dq_kernel.cu:422): delta[bh][n] = sum_d o*do (fp32),
  * then dq for every q-block.  `delta` is an output the dK/dV call reuses. */
+/* Head dim 128 with 64-row q and kv blocks runs on pairs of SMs (clusters of two
+ * CTAs, tcgen05 cta_group::2) in both backward calls; FTK_DQ_2CTA=0 and
+ * FTK_DKV_2CTA=0 select the one-CTA kernels that serve every other shape. */
 int ftk_sparse_bwd_dq(const void* q, const void* k, const void* v, const void* o, const void* dout,
                       int dtype, int64_t B, int64_t H, int64_t N, int64_t D, int64_t sq_b,
                       int64_t sq_n, int64_t sq_h, int64_t sk_b, int64_t sk_n, int64_t sk_h,

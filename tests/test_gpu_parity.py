@@ -340,6 +340,37 @@ def test_attention_blocks_up_to_128(ftk, g, kvb, qpad, kvpad, dtype):
     _close(v.grad.float().cpu().numpy(), wv, what="dV", stragglers=lax)
 
 
+def test_pair_kernels_agree_with_one_cta_kernels(ftk, monkeypatch):
+    """Head dim 128 with 64-row blocks runs on pairs of SMs (cta_group::2); the
+    one-CTA kernels (FTK_FWD_2CTA / FTK_DQ_2CTA / FTK_DKV_2CTA = 0) serve every
+    other shape.  Same inputs through both: the backward kernels do the same
+    arithmetic per element, the forward differs only in rounding order."""
+    H, N, D, g, kvb = 3, 1000, 128, 64, 64
+    cfg = dict(B=2, N=N, H=H, D=D, dtype="bf16", seed=51, do_seed=52)
+    t = cases.make_inputs(cfg)
+    qpad, kvpad = (24, 0), (20, 4)
+    QM, M = (qpad[0] + N) // g, (kvpad[0] + N + kvpad[1]) // kvb
+    merged = _random_lists(np.random.default_rng(17), 2 * H, QM, M, 9).reshape(2, H, QM, 9)
+    mg = torch.from_numpy(merged).cuda()
+
+    def run():
+        q = t["q"].cuda().requires_grad_(True)
+        k = t["k"].cuda().requires_grad_(True)
+        v = t["v"].cuda().requires_grad_(True)
+        o, lse = ftk.flash_topk_attn(q, k, v, mg, None, H, g, kvb, kv_padding=kvpad,
+                                     q_padding=qpad)
+        o.backward(t["do"].cuda())
+        ftk.check_errors()
+        return [x.detach().float().cpu().numpy() for x in (o, lse, q.grad, k.grad, v.grad)]
+
+    pair = run()
+    for name in ("FTK_FWD_2CTA", "FTK_DQ_2CTA", "FTK_DKV_2CTA"):
+        monkeypatch.setenv(name, "0")
+    single = run()
+    for a, b, what in zip(pair, single, ("O", "lse", "dQ", "dK", "dV")):
+        _close(a, b, what=f"{what}: pair vs one-CTA kernel")
+
+
 def test_fwd_pipelined_redo_on_exponent_range(ftk, monkeypatch):
     """Later blocks beat a row's first block by far more than 2^80: the
     pipelined kernel flags those tiles and the exact kernel redoes them, so
