@@ -5,7 +5,7 @@
 //
 // Two kernels: the exact running-maximum kernel below (every supported shape
 // and dtype) and the pipelined fixed-reference kernel of sparse_fwd_pipe.cuh
-// (bf16, 64-row kv blocks), which ftk_sparse_fwd launches first when the
+// (64-row q and kv blocks), which ftk_sparse_fwd launches first when the
 // caller passes a workspace; the exact kernel then only redoes flagged CTAs.
 //
 // One CTA owns 128 consecutive virtual query rows = G q-blocks of one (batch,
@@ -456,17 +456,17 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
 namespace ftk {
 
-template <int D>
+template <int D, int FMT>
 static int launch_fwd_pipe(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                            const FwdParams& p, int64_t BH, cudaStream_t st) {
   constexpr int NCH = D / 64;
   const size_t smem = 1024 + NCH * 128 * 128 +
                       static_cast<size_t>(FP_KST + FP_VST) * NCH * 64 * 128;
-  if (cudaFuncSetAttribute(sparse_fwd_pipe_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (cudaFuncSetAttribute(sparse_fwd_pipe_kernel<D, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(smem)) != cudaSuccess)
     return FTK_ERR_CUDA;
   dim3 grid((p.QM + p.G - 1) / p.G, static_cast<unsigned>(BH));
-  sparse_fwd_pipe_kernel<D><<<grid, FP_THREADS, smem, st>>>(tq, tk, tv, p);
+  sparse_fwd_pipe_kernel<D, FMT><<<grid, FP_THREADS, smem, st>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
 }
 
@@ -552,11 +552,10 @@ extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int d
   e = encode_tmap_bnhd(&tv, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, kv_block_size);
   if (e) return e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // bf16, 64-row kv and q blocks and a workspace: the
+  // 64-row kv and q blocks and a workspace: the
   // pipelined kernel runs first and the exact kernel redoes the CTAs it flags.
   const char* env = getenv("FTK_FWD_PIPE");
-  const bool pipe = dtype == FTK_DTYPE_BF16 && kv_block_size == 64 &&
-                    q_block_size == 64 && workspace &&
+  const bool pipe = kv_block_size == 64 && q_block_size == 64 && workspace &&
                     workspace_bytes >= ftk_sparse_fwd_workspace(B, H, QM, q_block_size) &&
                     !(env && env[0] == '0');
   if (pipe) {
@@ -568,15 +567,27 @@ extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int d
       e = encode_tmap_bnhd(&tk32, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, 32);
       if (e) return e;
       const size_t smem2 = 1024 + 2 * 128 * 128 + static_cast<size_t>(FP2_KST + FP2_VST) * 8192;
-      if (cudaFuncSetAttribute(sparse_fwd_pipe2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(smem2)) != cudaSuccess)
-        return FTK_ERR_CUDA;
       dim3 grid2(2 * ((QM + 3) / 4), static_cast<unsigned>(B * H));
-      sparse_fwd_pipe2_kernel<<<grid2, FP_THREADS, smem2, st>>>(tq, tk32, tv, p);
+      if (dtype == FTK_DTYPE_BF16) {
+        if (cudaFuncSetAttribute(sparse_fwd_pipe2_kernel<1>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem2)) != cudaSuccess)
+          return FTK_ERR_CUDA;
+        sparse_fwd_pipe2_kernel<1><<<grid2, FP_THREADS, smem2, st>>>(tq, tk32, tv, p);
+      } else {
+        if (cudaFuncSetAttribute(sparse_fwd_pipe2_kernel<0>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem2)) != cudaSuccess)
+          return FTK_ERR_CUDA;
+        sparse_fwd_pipe2_kernel<0><<<grid2, FP_THREADS, smem2, st>>>(tq, tk32, tv, p);
+      }
       e = cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+    } else if (dtype == FTK_DTYPE_BF16) {
+      e = (D == 64) ? launch_fwd_pipe<64, 1>(tq, tk, tv, p, B * H, st)
+                    : launch_fwd_pipe<128, 1>(tq, tk, tv, p, B * H, st);
     } else {
-      e = (D == 64) ? launch_fwd_pipe<64>(tq, tk, tv, p, B * H, st)
-                    : launch_fwd_pipe<128>(tq, tk, tv, p, B * H, st);
+      e = (D == 64) ? launch_fwd_pipe<64, 0>(tq, tk, tv, p, B * H, st)
+                    : launch_fwd_pipe<128, 0>(tq, tk, tv, p, B * H, st);
     }
     if (e) return e;
     p.redo_out = nullptr;

@@ -1,5 +1,4 @@
-// Deeply pipelined forward kernel for bf16 with 64-row kv blocks and 64-row
-// q-blocks.  Included by sparse_fwd.cu (shares FwdParams).
+// Deeply pipelined forward kernel for 64-row kv blocks and 64-row q-blocks.  Included by sparse_fwd.cu (shares FwdParams).
 //
 // The exact kernel keeps a running maximum per softmax group, which ties every
 // P tile to its group's accumulator: two groups, two O accumulators, two S
@@ -11,7 +10,8 @@
 // softmax groups work on four S buffers at once:
 //   TMEM columns  Q 0..63 | S/P buffers 64,128,192,256 | O 320..447
 // bf16 and fp32 share the exponent range, so a later block may exceed the
-// reference by up to 2^80 before anything overflows; a row whose tile sum
+// reference by up to 2^80 before anything overflows (fp16: 2^15, P must stay
+// below 65504); a row whose tile sum
 // passes that bound marks its CTA's word in `redo_out`, and the exact kernel,
 // launched behind this one, recomputes exactly those CTAs (all others return
 // on their first instruction).
@@ -25,14 +25,24 @@ constexpr int FP_KST = 4;         // K tiles in the ring (free again once S is c
 constexpr int FP_VST = 6;         // V tiles in the ring (held until P V has run)
 constexpr int FP_COL_S = 64;
 constexpr int FP_COL_O = 320;
-constexpr float FP_OVERFLOW = 1.2089258196146292e24f;  // 2^80
+// A tile's row sum of P above this marks the CTA for the exact kernel: 2^80 for
+// bf16 (fp32 exponent range), 2^15 for fp16 (P itself must stay below 65504).
+template <int FMT>
+__device__ __forceinline__ float fp_overflow_bound() {
+  return FMT == 1 ? 1.2089258196146292e24f : 32768.f;
+}
 
-__device__ __forceinline__ uint32_t bf16x2_bits(float a, float b) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+template <int FMT>
+__device__ __forceinline__ uint32_t pack16(float a, float b) {
+  if (FMT == 1) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int D>
+template <int D, int FMT>
 __global__ void __launch_bounds__(FP_THREADS, 1)
 sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
                        const __grid_constant__ CUtensorMap tm_k,
@@ -169,8 +179,8 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
   } else if (warp == 1) {
     // -------------------------------------------------------- UMMA issuer
     if (n > 0) {
-      const uint32_t idesc_s = umma_idesc(128, KVB, 1, 0, 0);
-      const uint32_t idesc_pv = umma_idesc(128, D, 1, 0, 1);
+      const uint32_t idesc_s = umma_idesc(128, KVB, FMT, 0, 0);
+      const uint32_t idesc_pv = umma_idesc(128, D, FMT, 0, 1);
       const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sK), 16, 1024);
       const uint64_t vdesc0 = smem_desc_sw128(smem_u32(sV), CHUNK, 1024);
       bool ok = mbar_wait(bar_qt, 0, w, FTK_DEV_TIMEOUT_MMA);
@@ -335,7 +345,7 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
                 make_float2(__uint_as_float(v0[x]), __uint_as_float(v0[x + 1])), c2, nm);
             const float2 e = make_float2(fast_exp2(t.x), fast_exp2(t.y));
             acc = __fadd2_rn(acc, e);
-            pk[x >> 1] = bf16x2_bits(e.x, e.y);
+            pk[x >> 1] = pack16<FMT>(e.x, e.y);
           }
           tmem_st16(s_addr, pk);
 #pragma unroll
@@ -344,7 +354,7 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
                 make_float2(__uint_as_float(v1[x]), __uint_as_float(v1[x + 1])), c2, nm);
             const float2 e = make_float2(fast_exp2(t.x), fast_exp2(t.y));
             acc = __fadd2_rn(acc, e);
-            pk[x >> 1] = bf16x2_bits(e.x, e.y);
+            pk[x >> 1] = pack16<FMT>(e.x, e.y);
           }
           tmem_st16(s_addr + 16, pk);
         } else {
@@ -356,7 +366,7 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
               a1 = fast_exp2(fmaf(__uint_as_float(v0[x + 1]), c, -mref));
             acc.x += a0;
             acc.y += a1;
-            pk[x >> 1] = bf16x2_bits(a0, a1);
+            pk[x >> 1] = pack16<FMT>(a0, a1);
           }
           tmem_st16(s_addr, pk);
 #pragma unroll
@@ -368,12 +378,12 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
               b1 = fast_exp2(fmaf(__uint_as_float(v1[x + 1]), c, -mref));
             acc.x += b0;
             acc.y += b1;
-            pk[x >> 1] = bf16x2_bits(b0, b1);
+            pk[x >> 1] = pack16<FMT>(b0, b1);
           }
           tmem_st16(s_addr + 16, pk);
         }
         const float lt = acc.x + acc.y;
-        if (!(lt <= FP_OVERFLOW)) ovf = true;   // also catches NaN
+        if (!(lt <= fp_overflow_bound<FMT>())) ovf = true;   // also catches NaN
         l += lt;
       } else {
         uint32_t z[16];
@@ -419,7 +429,7 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
         for (int x = 0; x < QUART; x += 2) {
           const float a = have ? __uint_as_float(ov[x]) * inv : 0.f;
           const float b = have ? __uint_as_float(ov[x + 1]) * inv : 0.f;
-          pk[x >> 1] = bf16x2_bits(a, b);
+          pk[x >> 1] = pack16<FMT>(a, b);
         }
         uint4* dst = reinterpret_cast<uint4*>(orow + c0 * 2);
 #pragma unroll

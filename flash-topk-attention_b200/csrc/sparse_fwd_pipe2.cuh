@@ -23,6 +23,7 @@ namespace ftk {
 constexpr int FP2_KST = 6;   // K half tiles (8 KB) in the ring
 constexpr int FP2_VST = 8;   // V half tiles (8 KB) in the ring
 
+template <int FMT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FP_THREADS, 1)
 sparse_fwd_pipe2_kernel(const __grid_constant__ CUtensorMap tm_q,
                         const __grid_constant__ CUtensorMap tm_k32,
@@ -187,8 +188,8 @@ sparse_fwd_pipe2_kernel(const __grid_constant__ CUtensorMap tm_q,
   } else if (warp == 1) {
     // ----------------------------- CTA 0: UMMA issuer for the CTA pair
     if (n > 0) {
-      const uint32_t idesc_s = umma_idesc(256, KVB, 1, 0, 0);
-      const uint32_t idesc_pv = umma_idesc(256, D, 1, 0, 1);
+      const uint32_t idesc_s = umma_idesc(256, KVB, FMT, 0, 0);
+      const uint32_t idesc_pv = umma_idesc(256, D, FMT, 0, 1);
       const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sK), 16, 1024);
       const uint64_t vdesc0 = smem_desc_sw128(smem_u32(sV), 8192, 1024);
       bool ok = mbar_wait(bar_qt, 0, w, FTK_DEV_TIMEOUT_MMA);
@@ -357,7 +358,7 @@ sparse_fwd_pipe2_kernel(const __grid_constant__ CUtensorMap tm_q,
                 make_float2(__uint_as_float(v0[x]), __uint_as_float(v0[x + 1])), c2, nm);
             const float2 e = make_float2(fast_exp2(t.x), fast_exp2(t.y));
             acc = __fadd2_rn(acc, e);
-            pk[x >> 1] = bf16x2_bits(e.x, e.y);
+            pk[x >> 1] = pack16<FMT>(e.x, e.y);
           }
           tmem_st16(s_addr, pk);
 #pragma unroll
@@ -366,7 +367,7 @@ sparse_fwd_pipe2_kernel(const __grid_constant__ CUtensorMap tm_q,
                 make_float2(__uint_as_float(v1[x]), __uint_as_float(v1[x + 1])), c2, nm);
             const float2 e = make_float2(fast_exp2(t.x), fast_exp2(t.y));
             acc = __fadd2_rn(acc, e);
-            pk[x >> 1] = bf16x2_bits(e.x, e.y);
+            pk[x >> 1] = pack16<FMT>(e.x, e.y);
           }
           tmem_st16(s_addr + 16, pk);
         } else {
@@ -378,7 +379,7 @@ sparse_fwd_pipe2_kernel(const __grid_constant__ CUtensorMap tm_q,
               a1 = fast_exp2(fmaf(__uint_as_float(v0[x + 1]), c, -mref));
             acc.x += a0;
             acc.y += a1;
-            pk[x >> 1] = bf16x2_bits(a0, a1);
+            pk[x >> 1] = pack16<FMT>(a0, a1);
           }
           tmem_st16(s_addr, pk);
 #pragma unroll
@@ -390,12 +391,12 @@ sparse_fwd_pipe2_kernel(const __grid_constant__ CUtensorMap tm_q,
               b1 = fast_exp2(fmaf(__uint_as_float(v1[x + 1]), c, -mref));
             acc.x += b0;
             acc.y += b1;
-            pk[x >> 1] = bf16x2_bits(b0, b1);
+            pk[x >> 1] = pack16<FMT>(b0, b1);
           }
           tmem_st16(s_addr + 16, pk);
         }
         const float lt = acc.x + acc.y;
-        if (!(lt <= FP_OVERFLOW)) ovf = true;   // also catches NaN
+        if (!(lt <= fp_overflow_bound<FMT>())) ovf = true;   // also catches NaN
         l += lt;
       } else {
         uint32_t z[16];
@@ -440,7 +441,7 @@ sparse_fwd_pipe2_kernel(const __grid_constant__ CUtensorMap tm_q,
         for (int x = 0; x < QUART; x += 2) {
           const float a = have ? __uint_as_float(ov[x]) * inv : 0.f;
           const float b = have ? __uint_as_float(ov[x + 1]) * inv : 0.f;
-          pk[x >> 1] = bf16x2_bits(a, b);
+          pk[x >> 1] = pack16<FMT>(a, b);
         }
         uint4* dst = reinterpret_cast<uint4*>(orow + c0 * 2);
 #pragma unroll

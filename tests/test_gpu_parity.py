@@ -234,18 +234,21 @@ def _random_lists(rng, BH, QM, M, width, empty_every=5):
     return merged
 
 
-@pytest.mark.parametrize("g,D,N,qpad,kvpad", [
-    (64, 128, 1000, (24, 0), (20, 4)),
-    (64, 128, 1024, (0, 0), (0, 0)),
-    (64, 64, 777, (0, 55), (0, 55)),
+@pytest.mark.parametrize("g,D,N,qpad,kvpad,dtype", [
+    (64, 128, 1000, (24, 0), (20, 4), "bf16"),
+    (64, 128, 1024, (0, 0), (0, 0), "bf16"),
+    (64, 64, 777, (0, 55), (0, 55), "bf16"),
+    (64, 128, 1000, (24, 0), (20, 4), "fp16"),
+    (64, 64, 777, (0, 55), (0, 55), "fp16"),
 ])
-def test_fwd_pipelined_kernel(ftk, g, D, N, qpad, kvpad, monkeypatch):
-    """bf16 / 64-row kv blocks take the pipelined forward kernel (fixed
-    reference exponent, four tiles in flight).  Ragged lengths, virtual
-    padding, empty and unequal neighbouring lists against the oracle, and
-    against the exact kernel alone (FTK_FWD_PIPE=0)."""
+def test_fwd_pipelined_kernel(ftk, g, D, N, qpad, kvpad, dtype, monkeypatch):
+    """64-row q and kv blocks take the pipelined forward kernel (fixed
+    reference exponent, four tiles in flight; on pairs of SMs at head dim
+    128).  Ragged lengths, virtual padding, empty and unequal neighbouring
+    lists against the oracle, and against the exact kernel alone
+    (FTK_FWD_PIPE=0)."""
     H, kvb = 3, 64
-    cfg = dict(B=2, N=N, H=H, D=D, dtype="bf16", seed=11, do_seed=12)
+    cfg = dict(B=2, N=N, H=H, D=D, dtype=dtype, seed=11, do_seed=12)
     t = cases.make_inputs(cfg)
     x = {k: v.float().numpy() for k, v in t.items()}
     QM = (qpad[0] + N + qpad[1]) // g
@@ -371,14 +374,16 @@ def test_pair_kernels_agree_with_one_cta_kernels(ftk, monkeypatch):
         _close(a, b, what=f"{what}: pair vs one-CTA kernel")
 
 
-def test_fwd_pipelined_redo_on_exponent_range(ftk, monkeypatch):
-    """Later blocks beat a row's first block by far more than 2^80: the
-    pipelined kernel flags those tiles and the exact kernel redoes them, so
-    the flagged tiles equal the exact kernel's output bit for bit."""
+@pytest.mark.parametrize("dtype,kscale", [("bf16", 30.0), ("fp16", 4.0)])
+def test_fwd_pipelined_redo_on_exponent_range(ftk, monkeypatch, dtype, kscale):
+    """Later blocks beat a row's first block by more than the format allows
+    (2^80 for bf16, 2^15 for fp16): the pipelined kernel flags those tiles and
+    the exact kernel redoes them, so the flagged tiles equal the exact
+    kernel's output bit for bit."""
     H, g, kvb, N, D = 2, 64, 64, 512, 128
-    cfg = dict(B=1, N=N, H=H, D=D, dtype="bf16", seed=21, do_seed=22)
+    cfg = dict(B=1, N=N, H=H, D=D, dtype=dtype, seed=21, do_seed=22)
     t = cases.make_inputs(cfg)
-    t["k"][:, 256:] *= 30.0             # logits of blocks 4..7 reach hundreds of nats
+    t["k"][:, 256:] *= kscale           # logits of blocks 4..7 leave the safe range
     t["q"] *= 2.0
     x = {k: v.float().numpy() for k, v in t.items()}
     QM = M = N // 64
@@ -389,7 +394,7 @@ def test_fwd_pipelined_redo_on_exponent_range(ftk, monkeypatch):
     o, lse = ftk.flash_topk_attn(*args)
     ftk.check_errors()
     wo, wl = orc.sparse_attn_fwd(x["q"], x["k"], x["v"], merged, H, g, kvb)
-    assert np.abs(wl).max() > 100.0
+    assert np.abs(wl).max() > (100.0 if dtype == "bf16" else 20.0)
     assert torch.isfinite(o).all() and torch.isfinite(lse).all()
     # one-hot softmax rows: the error is the bf16 rounding of two competing P
     _close(o.float().cpu().numpy(), wo, atol=2e-2, what="O")
