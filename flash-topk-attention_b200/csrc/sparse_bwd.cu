@@ -76,6 +76,41 @@ __device__ __forceinline__ void ds_pairs(const uint32_t (&sv)[32], const uint32_
   }
 }
 
+// P^T = 2^(c s - lse2) and dS^T = P^T (dp - delta) for 16 columns (= q rows) of
+// one kv row, two columns per instruction; lse2 / delta of the columns come
+// NEGATED from shared memory, one 16-byte broadcast load per four columns.
+template <int FMT>
+__device__ __forceinline__ void pt_pairs(const uint32_t (&sv)[16], const uint32_t (&dv)[16],
+                                         const float4* nl4, const float4* nd4, float c,
+                                         uint32_t (&pp)[8], uint32_t (&pd)[8]) {
+  const float2 c2 = make_float2(c, c);
+#pragma unroll
+  for (int x = 0; x < 16; x += 4) {
+    const float4 lq = nl4[x >> 2];
+    const float4 dq = nd4[x >> 2];
+#pragma unroll
+    for (int y = 0; y < 4; y += 2) {
+      const float2 nl = y == 0 ? make_float2(lq.x, lq.y) : make_float2(lq.z, lq.w);
+      const float2 nd = y == 0 ? make_float2(dq.x, dq.y) : make_float2(dq.z, dq.w);
+      const float2 t = __ffma2_rn(
+          make_float2(__uint_as_float(sv[x + y]), __uint_as_float(sv[x + y + 1])), c2, nl);
+      const float2 pr = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+      const float2 dd = __fadd2_rn(
+          make_float2(__uint_as_float(dv[x + y]), __uint_as_float(dv[x + y + 1])), nd);
+      const float2 ds = __fmul2_rn(pr, dd);
+      if (FMT == 1) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(pr.x, pr.y), b = __floats2bfloat162_rn(ds.x, ds.y);
+        pp[(x + y) >> 1] = *reinterpret_cast<uint32_t*>(&a);
+        pd[(x + y) >> 1] = *reinterpret_cast<uint32_t*>(&b);
+      } else {
+        __half2 a = __floats2half2_rn(pr.x, pr.y), b = __floats2half2_rn(ds.x, ds.y);
+        pp[(x + y) >> 1] = *reinterpret_cast<uint32_t*>(&a);
+        pd[(x + y) >> 1] = *reinterpret_cast<uint32_t*>(&b);
+      }
+    }
+  }
+}
+
 constexpr int BW_THREADS = 576;  // 2 + 2 x 8 warps
 constexpr int BW_MAX_STAGES = 4;
 constexpr int DQ_KST = 7;        // dQ kernel: K tiles in the ring (held until dQ += dS K ran)
@@ -664,9 +699,9 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
       if (ct < p.g) {
         const int t = row0 + ct;
         float l2 = 0.f, dl = 0.f;
-        if (t >= 0 && t < p.N) {
-          l2 = p.lse[static_cast<int64_t>(bh) * p.N + t] * 1.4426950408889634f;
-          dl = p.delta[static_cast<int64_t>(bh) * p.N + t];
+        if (t >= 0 && t < p.N) {   // staged negated: the packed fma / add take them as they are
+          l2 = -p.lse[static_cast<int64_t>(bh) * p.N + t] * 1.4426950408889634f;
+          dl = -p.delta[static_cast<int64_t>(bh) * p.N + t];
         }
         s_lse2[wg][pb][ct] = l2;
         s_delta[wg][pb][ct] = dl;
@@ -694,21 +729,8 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
         tmem_ld16(dp_addr + c0, dv);
         tmem_wait_ld();
         if (fast) {
-#pragma unroll
-          for (int x = 0; x < 16; x += 4) {
-            const float4 lq = l4[(c0 + x) >> 2];
-            const float4 dq = d4[(c0 + x) >> 2];
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[x + 0]), c, -lq.x));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[x + 1]), c, -lq.y));
-            const float p2 = fast_exp2(fmaf(__uint_as_float(sv[x + 2]), c, -lq.z));
-            const float p3 = fast_exp2(fmaf(__uint_as_float(sv[x + 3]), c, -lq.w));
-            pp[x >> 1] = pack2(p0, p1, p.fmt);
-            pp[(x >> 1) + 1] = pack2(p2, p3, p.fmt);
-            pd[x >> 1] = pack2(p0 * (__uint_as_float(dv[x + 0]) - dq.x),
-                               p1 * (__uint_as_float(dv[x + 1]) - dq.y), p.fmt);
-            pd[(x >> 1) + 1] = pack2(p2 * (__uint_as_float(dv[x + 2]) - dq.z),
-                                     p3 * (__uint_as_float(dv[x + 3]) - dq.w), p.fmt);
-          }
+          if (p.fmt == 1) pt_pairs<1>(sv, dv, l4 + (c0 >> 2), d4 + (c0 >> 2), c, pp, pd);
+          else pt_pairs<0>(sv, dv, l4 + (c0 >> 2), d4 + (c0 >> 2), c, pp, pd);
         } else {
 #pragma unroll
           for (int x = 0; x < 16; x += 4) {
@@ -720,9 +742,9 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
             for (int y = 0; y < 4; y++) {
               const bool on = act && c0 + x + y >= lo && c0 + x + y < hi;
-              const float pr = on ? fast_exp2(fmaf(__uint_as_float(sv[x + y]), c, -ls[y])) : 0.f;
+              const float pr = on ? fast_exp2(fmaf(__uint_as_float(sv[x + y]), c, ls[y])) : 0.f;
               pv[y] = pr;
-              dsv[y] = pr * (__uint_as_float(dv[x + y]) - ds[y]);
+              dsv[y] = pr * (__uint_as_float(dv[x + y]) + ds[y]);
             }
             pp[x >> 1] = pack2(pv[0], pv[1], p.fmt);
             pp[(x >> 1) + 1] = pack2(pv[2], pv[3], p.fmt);
