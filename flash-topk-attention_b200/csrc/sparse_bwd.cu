@@ -890,8 +890,11 @@ extern "C" int ftk_sparse_bwd_dq(
   if ((e = encode_tmap_bnhd(&tv, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, kv_block_size)))
     return e;
   // head dim 128 with 64-row q and kv blocks: the kernel on pairs of SMs
+  // (pairs walk the union of four lists: only when the lists can cover a good
+  // part of the blocks, see ftk_sparse_fwd)
   const char* env2 = getenv("FTK_DQ_2CTA");
-  if (D == 128 && q_block_size == 64 && kv_block_size == 64 && !(env2 && env2[0] == '0')) {
+  if (D == 128 && q_block_size == 64 && kv_block_size == 64 &&
+      4 * static_cast<int64_t>(W) >= Mkv && !(env2 && env2[0] == '0')) {
     CUtensorMap tk32, tv32;
     if ((e = encode_tmap_bnhd(&tk32, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, 32))) return e;
     if ((e = encode_tmap_bnhd(&tv32, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, 32))) return e;
@@ -940,7 +943,7 @@ extern "C" int ftk_sparse_bwd_dkv(
     const int32_t* sorted_kv, int QM, int M, int q_block_size, int kv_block_size, int q_pad_head,
     int kv_pad_head, float scale, const float* lse, const float* delta, void* dk, int64_t sdk_b,
     int64_t sdk_n, int64_t sdk_h, void* dv, int64_t sdv_b, int64_t sdv_n, int64_t sdv_h,
-    int32_t* status, void* stream) {
+    int fwd_list_width, int32_t* status, void* stream) {
   (void)sorted_kv;  // tiles are issued in block order; kept for interface parity
   if (!q || !k || !v || !dout || !reverse_idx || !reverse_counts || !lse || !delta)
     return FTK_ERR_BAD_ARG;
@@ -991,7 +994,9 @@ extern "C" int ftk_sparse_bwd_dkv(
   if ((e = encode_tmap_bnhd(&tv, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, 128))) return e;
   // head dim 128 with 64-row q and kv blocks: the kernel on pairs of SMs
   const char* env2 = getenv("FTK_DKV_2CTA");
-  if (D == 128 && q_block_size == 64 && kv_block_size == 64 && !(env2 && env2[0] == '0')) {
+  const bool long_lists = fwd_list_width <= 0 || 4 * static_cast<int64_t>(fwd_list_width) >= M;
+  if (D == 128 && q_block_size == 64 && kv_block_size == 64 && long_lists &&
+      !(env2 && env2[0] == '0')) {
     CUtensorMap tq32, tdo32;
     if ((e = encode_tmap_bnhd(&tq32, q, dtype, B, N, H, D, sq_b, sq_n, sq_h, 64, 32))) return e;
     if ((e = encode_tmap_bnhd(&tdo32, dout, dtype, B, N, H, D, sdo_b, sdo_n, sdo_h, 64, 32)))

@@ -561,7 +561,10 @@ extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int d
   if (pipe) {
     p.redo_out = static_cast<int*>(workspace);
     const char* env2 = getenv("FTK_FWD_2CTA");
-    if (D == 128 && !(env2 && env2[0] == '0')) {
+    // Pairs walk the union of four lists: worth it when the lists can cover a
+    // good part of the blocks (then the unions of two and of four are about
+    // the same length); short lists keep the one-CTA kernel's unions of two.
+    if (D == 128 && 4 * static_cast<int64_t>(W) >= Mkv && !(env2 && env2[0] == '0')) {
       // head dim 128: the same kernel on pairs of SMs
       CUtensorMap tk32;
       e = encode_tmap_bnhd(&tk32, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, 32);

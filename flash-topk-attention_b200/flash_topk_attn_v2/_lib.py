@@ -48,7 +48,7 @@ SIGNATURES = {
                                 i32, i32, i32, i32, f32, vp, vp, vp, *_STRIDES3, vp, vp]),
     "ftk_sparse_bwd_dkv": (i32, [vp, vp, vp, vp, i32, i64, i64, i64, i64, *_STRIDES3, *_STRIDES3,
                                  *_STRIDES3, *_STRIDES3, vp, vp, vp, i32, i32, i32, i32, i32,
-                                 i32, f32, vp, vp, vp, *_STRIDES3, vp, *_STRIDES3, vp, vp]),
+                                 i32, f32, vp, vp, vp, *_STRIDES3, vp, *_STRIDES3, i32, vp, vp]),
 }
 
 

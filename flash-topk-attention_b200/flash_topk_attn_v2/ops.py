@@ -477,7 +477,7 @@ class FlashSparseAttnFunc(torch.autograd.Function):
             ptr(qq), ptr(kk), ptr(vv), ptr(do), dt, B, H, N, D,
             sq_b, sq_n, sq_h, sk_b, sk_n, sk_h, sv_b, sv_n, sv_h, sdo_b, sdo_n, sdo_h,
             ptr(rev), ptr(rc), ptr(skv), QM, M, g, kvb, qph, kph, scale,
-            ptr(lse), ptr(delta), ptr(dk), N * C, C, D, ptr(dv), N * C, C, D, ptr(status), st)
+            ptr(lse), ptr(delta), ptr(dk), N * C, C, D, ptr(dv), N * C, C, D, W, ptr(status), st)
         _count(1)
         _after(dev)
         return dq, dk, dv, None, None, None, None, None, None, None, None

@@ -216,7 +216,10 @@ int ftk_sparse_bwd_dq(const void* q, const void* k, const void* v, const void* o
 
 /* Replaces sparse_attn_bwd_dkv_launch (csrc/sparse_attn_bwd_dkv.cpp:3-16,
  * csrc/sparse_attn_bwd_dkv_kernel.cu:438): dk, dv per kv block from the
- * reverse index (one writer per kv row, no atomics). */
+ * reverse index (one writer per kv row, no atomics).  `fwd_list_width` is the
+ * width W of the merged_idx lists the reverse index was built from (0 if
+ * unknown); it only helps to choose between the kernel on pairs of SMs (lists
+ * that can cover a good part of the blocks: 4 W >= M) and the one-CTA kernel. */
 int ftk_sparse_bwd_dkv(const void* q, const void* k, const void* v, const void* dout, int dtype,
                        int64_t B, int64_t H, int64_t N, int64_t D, int64_t sq_b, int64_t sq_n,
                        int64_t sq_h, int64_t sk_b, int64_t sk_n, int64_t sk_h, int64_t sv_b,
@@ -226,7 +229,7 @@ int ftk_sparse_bwd_dkv(const void* q, const void* k, const void* v, const void* 
                        int kv_block_size, int q_pad_head, int kv_pad_head, float scale,
                        const float* lse, const float* delta, void* dk, int64_t sdk_b,
                        int64_t sdk_n, int64_t sdk_h, void* dv, int64_t sdv_b, int64_t sdv_n,
-                       int64_t sdv_h, int32_t* status, void* stream);
+                       int64_t sdv_h, int fwd_list_width, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }
