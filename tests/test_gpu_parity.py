@@ -409,6 +409,38 @@ def test_fwd_pipelined_redo_on_exponent_range(ftk, monkeypatch, dtype, kscale):
     _close(o.float().cpu().numpy(), o2.float().cpu().numpy(), what="O vs exact")
 
 
+def test_pair_kernels_with_empty_pairs(ftk):
+    """Head dim 128, 64-row blocks, N = 512: eight q-blocks = two CTA pairs.
+    Head 0: the second pair's q-blocks list nothing (forward / dQ pair with no
+    work) and nobody lists kv blocks 4..7 (dK/dV pair with no work); head 1:
+    only one q-block of each pair attends."""
+    H, N, D, g, kvb = 2, 512, 128, 64, 64
+    cfg = dict(B=1, N=N, H=H, D=D, dtype="bf16", seed=61, do_seed=62)
+    t = cases.make_inputs(cfg)
+    x = {k: v.float().numpy() for k, v in t.items()}
+    QM = M = 8
+    merged = np.full((1, H, QM, 8), -1, dtype=np.int32)
+    merged[0, 0, :4, :4] = [[0, 1, 2, 3], [3, 1, 0, 2], [2, 0, 3, 1], [1, 3, 2, 0]]
+    merged[0, 1, 1, :3] = [7, 0, 4]
+    merged[0, 1, 6, :2] = [5, 2]
+    q = t["q"].cuda().requires_grad_(True)
+    k = t["k"].cuda().requires_grad_(True)
+    v = t["v"].cuda().requires_grad_(True)
+    o, lse = ftk.flash_topk_attn(q, k, v, torch.from_numpy(merged).cuda(), None, H, g, kvb)
+    o.backward(t["do"].cuda())
+    ftk.check_errors()
+    wo, wl = orc.sparse_attn_fwd(x["q"], x["k"], x["v"], merged, H, g, kvb)
+    _close(o.detach().float().cpu().numpy(), wo, what="O")
+    _close(lse.cpu().numpy(), wl, what="lse")
+    assert torch.isinf(lse[0, 0, 256:]).all() and (o[0, 256:, :D] == 0).all()
+    wq, wk, wv = orc.sparse_attn_bwd(x["q"], x["k"], x["v"], o.detach().float().cpu().numpy(), wl,
+                                     x["do"], merged, H, g, kvb)
+    _close(q.grad.float().cpu().numpy(), wq, what="dQ", stragglers=1e-4)
+    _close(k.grad.float().cpu().numpy(), wk, what="dK", stragglers=1e-4)
+    _close(v.grad.float().cpu().numpy(), wv, what="dV", stragglers=1e-4)
+    assert (k.grad[0, 256:, :D] == 0).all() and (v.grad[0, 256:, :D] == 0).all()
+
+
 def test_score_overflow_fallback(ftk):
     """Logits far above the first key tile's maximum overflow the single-pass
     sums; the exact two-pass fallback must take over."""
