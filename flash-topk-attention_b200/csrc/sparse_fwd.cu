@@ -552,10 +552,10 @@ extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int d
   e = encode_tmap_bnhd(&tv, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, kv_block_size);
   if (e) return e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // 64-row kv and q blocks and a workspace: the
+  // 64-row kv blocks, q blocks of 64 or 32 rows and a workspace: the
   // pipelined kernel runs first and the exact kernel redoes the CTAs it flags.
   const char* env = getenv("FTK_FWD_PIPE");
-  const bool pipe = kv_block_size == 64 && q_block_size == 64 && workspace &&
+  const bool pipe = kv_block_size == 64 && (q_block_size == 64 || q_block_size == 32) && workspace &&
                     workspace_bytes >= ftk_sparse_fwd_workspace(B, H, QM, q_block_size) &&
                     !(env && env[0] == '0');
   if (pipe) {
@@ -564,7 +564,8 @@ extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int d
     // Pairs walk the union of four lists: worth it when the lists can cover a
     // good part of the blocks (then the unions of two and of four are about
     // the same length); short lists keep the one-CTA kernel's unions of two.
-    if (D == 128 && 4 * static_cast<int64_t>(W) >= Mkv && !(env2 && env2[0] == '0')) {
+    if (D == 128 && q_block_size == 64 && 4 * static_cast<int64_t>(W) >= Mkv &&
+        !(env2 && env2[0] == '0')) {
       // head dim 128: the same kernel on pairs of SMs
       CUtensorMap tk32;
       e = encode_tmap_bnhd(&tk32, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, 32);

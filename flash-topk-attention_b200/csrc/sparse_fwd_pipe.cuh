@@ -1,4 +1,5 @@
-// Deeply pipelined forward kernel for 64-row kv blocks and 64-row q-blocks.  Included by sparse_fwd.cu (shares FwdParams).
+// Deeply pipelined forward kernel for 64-row kv blocks and q-blocks of 64 or 32
+// rows.  Included by sparse_fwd.cu (shares FwdParams).
 //
 // The exact kernel keeps a running maximum per softmax group, which ties every
 // P tile to its group's accumulator: two groups, two O accumulators, two S
@@ -63,7 +64,7 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
   __shared__ int s_ovf;
-  __shared__ int s_first[2];
+  __shared__ int s_first[4];
   __shared__ float s_l[FP_GROUPS][128];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -116,7 +117,7 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int n = build_union(un, p.merged + (static_cast<int64_t>(bh) * p.QM + m0) * p.W, p.W,
                             groups, p.W, nullptr, p.Mkv, p.status);
   // lowest listed block of each q-block: its scores give the rows' reference
-  if (warp < 2) {
+  if (warp < 4) {
     int best = 0x7fffffff;
     if (warp < groups) {
 #pragma unroll
@@ -134,18 +135,24 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
   const uint32_t tmem = tmem_base_s;
   WaitCtx w{&abort_flag, p.status};
 
-  // prologue entries: one per q-block with a non-empty list
+  // prologue entries: one per q-block of the tile (two of 64 rows or four of
+  // 32) with a non-empty list; entry e goes through S buffer e
   int npro = 0;
-  int pro_id[2] = {0, 0};
-  int pro_buf[2] = {-1, -1};
+  int pro_id[4] = {0, 0, 0, 0};
+  int pro_buf[4] = {-1, -1, -1, -1};
 #pragma unroll
-  for (int g = 0; g < 2; g++) {
+  for (int g = 0; g < 4; g++) {
     if (g < groups && s_first[g] >= 0) {
-      if (npro == 0) pro_id[0] = s_first[g]; else pro_id[1] = s_first[g];
+#pragma unroll
+      for (int e = 0; e < 4; e++)
+        if (e == npro) pro_id[e] = s_first[g];
       pro_buf[g] = npro;
       npro++;
     }
   }
+  auto pro_block = [&](int e) {
+    return e == 0 ? pro_id[0] : e == 1 ? pro_id[1] : e == 2 ? pro_id[2] : pro_id[3];
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------- TMA producer
@@ -160,7 +167,7 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
         const int sk = j % FP_KST;
         if (!mbar_wait(bar_kempty(sk), ((j / FP_KST) & 1) ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
         const bool pro = j < npro;
-        const int id = pro ? (j == 0 ? pro_id[0] : pro_id[1]) : static_cast<int>(un.ids[j - npro]);
+        const int id = pro ? pro_block(j) : static_cast<int>(un.ids[j - npro]);
         const int tok0 = id * KVB - p.kv_pad_head;
         const uint32_t kb = smem_u32(sK) + sk * TILE;
         mbar_expect_tx(bar_kfull(sk), TILE);
@@ -250,7 +257,7 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
     const int gw = (warp - 2) >> 2;          // softmax group = S buffer it drains
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
-    const int grp = r / p.g;                 // warp-uniform: q-blocks are 64 rows
+    const int grp = r / p.g;                 // warp-uniform: q-blocks are 64 or 32 rows
     const int qrow = tile_row0 + r;
     const bool row_valid = (grp < groups) && qrow >= 0 && qrow < p.N;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -289,13 +296,14 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
       // Every warp waits for every prologue buffer, also the ones it does not
       // read: its later parity waits on those buffers must not start while
       // their first phase is still open.
-      const int pb = grp < 2 ? (grp == 0 ? pro_buf[0] : pro_buf[1]) : -1;
+      const int pb = grp == 0 ? pro_buf[0] : grp == 1 ? pro_buf[1] : grp == 2 ? pro_buf[2]
+                                                                               : pro_buf[3];
       for (int e = 0; ok && e < npro; e++)
         ok = mbar_wait(bar_sfull(e), 0, w, FTK_DEV_TIMEOUT_CONSUMER);
       if (ok && pb >= 0) {
         {
           tc_fence_after();
-          const int tok0 = (pb == 0 ? pro_id[0] : pro_id[1]) * KVB - p.kv_pad_head;
+          const int tok0 = pro_block(pb) * KVB - p.kv_pad_head;
           const int lo = max(0, -tok0), hi = min(KVB, p.N - tok0);
           uint32_t v0[32], v1[32];
           tmem_ld32(lane_addr + FP_COL_S + pb * 64, v0);

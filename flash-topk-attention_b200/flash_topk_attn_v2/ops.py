@@ -438,7 +438,7 @@ class FlashSparseAttnFunc(torch.autograd.Function):
             ptr(merged), QM, W, q_block_size, kv_block_size, q_pad_head, kv_pad_head,
             float(scale), ptr(o), N * C, C, D, ptr(lse), ptr(ws), ws_bytes,
             ptr(status_word(dev)), stream_ptr(dev))
-        piped = (kv_block_size == 64 and q_block_size == 64
+        piped = (kv_block_size == 64 and q_block_size in (32, 64)
                  and os.environ.get("FTK_FWD_PIPE", "1")[:1] != "0")
         _count(2 if piped else 1)
         _after(dev)

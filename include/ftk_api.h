@@ -181,7 +181,7 @@ int ftk_sort_by_count(const int32_t* counts, int64_t total, int max_count,
  * valid prefix of its row.  o in `dtype` with strides (so_*), lse fp32
  * [B*H][N] (natural log; -inf and o = 0 for an empty list).
  * `workspace` (ftk_sparse_fwd_workspace bytes, may be NULL) enables the
- * pipelined kernel for 64-row kv blocks and 64-row q-blocks (bf16 or fp16):
+ * pipelined kernel for 64-row kv blocks and q-blocks of 64 or 32 rows (bf16 or fp16):
  * it uses one fixed reference exponent per row, and the exact running-maximum
  * kernel, launched behind it, recomputes the tiles whose scores left the safe
  * exponent range (none on ordinary inputs).  Without a workspace only the
