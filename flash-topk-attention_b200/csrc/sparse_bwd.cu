@@ -129,6 +129,7 @@ struct BwdParams {
   void* out1;                //                  dKV kernel: dv
   int64_t s0_b, s0_n, s0_h, s1_b, s1_n, s1_h;
   int* status;
+  int kv_hdiv;               // query heads per kv head (grouped-query attention), 1 otherwise
 };
 
 // ---------------------------------------------------------------------- dQ
@@ -238,14 +239,16 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint32_t kb = smem_u32(sK) + sk * tile_bytes;
         mbar_expect_tx(bar_kfull(sk), tile_bytes);
         for (int c = 0; c < NCH; c++)
-          tma_load_4d(kb + c * kv_chunk_bytes, &tm_k, bar_kfull(sk), c * 64, h_idx, tok0, b_idx);
+          tma_load_4d(kb + c * kv_chunk_bytes, &tm_k, bar_kfull(sk), c * 64, h_idx / p.kv_hdiv,
+                      tok0, b_idx);
         // the V ring lies over the Q / dO tiles: wait until they sit in TMEM
         if (i == 0 && !mbar_wait(bar_qt, 0, w, FTK_DEV_TIMEOUT_TMA)) break;
         if (!mbar_wait(bar_vempty(sv), ((i / DQ_VST) & 1) ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
         const uint32_t vb = v_slot(sv);
         mbar_expect_tx(bar_vfull(sv), tile_bytes);
         for (int c = 0; c < NCH; c++)
-          tma_load_4d(vb + c * kv_chunk_bytes, &tm_v, bar_vfull(sv), c * 64, h_idx, tok0, b_idx);
+          tma_load_4d(vb + c * kv_chunk_bytes, &tm_v, bar_vfull(sv), c * 64, h_idx / p.kv_hdiv,
+                      tok0, b_idx);
       }
     }
   } else if (warp == 1) {
@@ -565,8 +568,10 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
     if (lane == 0 && n > 0) {
       mbar_expect_tx(bar_kv, 2 * ROW_TILE_BYTES);
       for (int c = 0; c < NCH; c++) {
-        tma_load_4d(smem_u32(sK) + c * 128 * 128, &tm_k, bar_kv, c * 64, h_idx, tile_tok0, b_idx);
-        tma_load_4d(smem_u32(sV) + c * 128 * 128, &tm_v, bar_kv, c * 64, h_idx, tile_tok0, b_idx);
+        tma_load_4d(smem_u32(sK) + c * 128 * 128, &tm_k, bar_kv, c * 64, h_idx / p.kv_hdiv,
+                    tile_tok0, b_idx);
+        tma_load_4d(smem_u32(sV) + c * 128 * 128, &tm_v, bar_kv, c * 64, h_idx / p.kv_hdiv,
+                    tile_tok0, b_idx);
       }
       for (int i = 0; i < n; i++) {
         const int s = i % NST;
@@ -835,7 +840,7 @@ using namespace ftk;
 
 extern "C" int ftk_sparse_bwd_dq(
     const void* q, const void* k, const void* v, const void* o, const void* dout, int dtype,
-    int64_t B, int64_t H, int64_t N, int64_t D, int64_t sq_b, int64_t sq_n, int64_t sq_h,
+    int64_t B, int64_t H, int64_t Hkv, int64_t N, int64_t D, int64_t sq_b, int64_t sq_n, int64_t sq_h,
     int64_t sk_b, int64_t sk_n, int64_t sk_h, int64_t sv_b, int64_t sv_n, int64_t sv_h,
     int64_t so_b, int64_t so_n, int64_t so_h, int64_t sdo_b, int64_t sdo_n, int64_t sdo_h,
     const int32_t* merged_idx, int QM, int W, int q_block_size, int kv_block_size, int q_pad_head,
@@ -846,6 +851,8 @@ extern "C" int ftk_sparse_bwd_dq(
   int e = bwd_common_checks(dtype, B, H, N, D, QM, q_block_size, kv_block_size, q_pad_head,
                             kv_pad_head);
   if (e) return e;
+  if (Hkv <= 0) Hkv = H;
+  if (H % Hkv != 0) return FTK_ERR_BAD_ARG;
   if (q_block_size > 128) return FTK_ERR_UNSUPPORTED;
   if (!aligned_out(dq, sdq_b, sdq_n, sdq_h)) return FTK_ERR_BAD_ARG;
   if ((so_b | so_n | so_h | sdo_b | sdo_n | sdo_h) & 1) return FTK_ERR_BAD_ARG;
@@ -881,13 +888,14 @@ extern "C" int ftk_sparse_bwd_dq(
   p.s0_n = sdq_n;
   p.s0_h = sdq_h;
   p.status = status;
+  p.kv_hdiv = static_cast<int>(H / Hkv);
 
   CUtensorMap tq, tdo, tk, tv;
   if ((e = encode_tmap_bnhd(&tq, q, dtype, B, N, H, D, sq_b, sq_n, sq_h, 64, 128))) return e;
   if ((e = encode_tmap_bnhd(&tdo, dout, dtype, B, N, H, D, sdo_b, sdo_n, sdo_h, 64, 128))) return e;
-  if ((e = encode_tmap_bnhd(&tk, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, kv_block_size)))
+  if ((e = encode_tmap_bnhd(&tk, k, dtype, B, N, Hkv, D, sk_b, sk_n, sk_h, 64, kv_block_size)))
     return e;
-  if ((e = encode_tmap_bnhd(&tv, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, kv_block_size)))
+  if ((e = encode_tmap_bnhd(&tv, v, dtype, B, N, Hkv, D, sv_b, sv_n, sv_h, 64, kv_block_size)))
     return e;
   // head dim 128 with 64-row q and kv blocks: the kernel on pairs of SMs
   // (pairs walk the union of four lists: only when the lists can cover a good
@@ -896,8 +904,8 @@ extern "C" int ftk_sparse_bwd_dq(
   if (D == 128 && q_block_size == 64 && kv_block_size == 64 &&
       4 * static_cast<int64_t>(W) >= Mkv && !(env2 && env2[0] == '0')) {
     CUtensorMap tk32, tv32;
-    if ((e = encode_tmap_bnhd(&tk32, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, 32))) return e;
-    if ((e = encode_tmap_bnhd(&tv32, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, 32))) return e;
+    if ((e = encode_tmap_bnhd(&tk32, k, dtype, B, N, Hkv, D, sk_b, sk_n, sk_h, 64, 32))) return e;
+    if ((e = encode_tmap_bnhd(&tv32, v, dtype, B, N, Hkv, D, sv_b, sv_n, sv_h, 64, 32))) return e;
     const size_t smem2 = 1024 + 2 * 2 * 128 * 128 + static_cast<size_t>(DQ2_STAGES) * 24576;
     dim3 grid2(2 * ((QM + 3) / 4), static_cast<unsigned>(B * H));
     if (dtype == FTK_DTYPE_BF16) {
@@ -937,7 +945,7 @@ extern "C" int ftk_sparse_bwd_dq(
 
 extern "C" int ftk_sparse_bwd_dkv(
     const void* q, const void* k, const void* v, const void* dout, int dtype, int64_t B, int64_t H,
-    int64_t N, int64_t D, int64_t sq_b, int64_t sq_n, int64_t sq_h, int64_t sk_b, int64_t sk_n,
+    int64_t Hkv, int64_t N, int64_t D, int64_t sq_b, int64_t sq_n, int64_t sq_h, int64_t sk_b, int64_t sk_n,
     int64_t sk_h, int64_t sv_b, int64_t sv_n, int64_t sv_h, int64_t sdo_b, int64_t sdo_n,
     int64_t sdo_h, const int32_t* reverse_idx, const int32_t* reverse_counts,
     const int32_t* sorted_kv, int QM, int M, int q_block_size, int kv_block_size, int q_pad_head,
@@ -950,6 +958,8 @@ extern "C" int ftk_sparse_bwd_dkv(
   int e = bwd_common_checks(dtype, B, H, N, D, QM, q_block_size, kv_block_size, q_pad_head,
                             kv_pad_head);
   if (e) return e;
+  if (Hkv <= 0) Hkv = H;
+  if (H % Hkv != 0) return FTK_ERR_BAD_ARG;
   if (q_block_size % 16 != 0 || q_block_size > 64) return FTK_ERR_UNSUPPORTED;
   if (QM > AT_MAX_BLOCKS) return FTK_ERR_UNSUPPORTED;
   if (M <= 0 || static_cast<int64_t>(M) * kv_block_size < kv_pad_head + N) return FTK_ERR_BAD_ARG;
@@ -984,14 +994,15 @@ extern "C" int ftk_sparse_bwd_dkv(
   p.s1_n = sdv_n;
   p.s1_h = sdv_h;
   p.status = status;
+  p.kv_hdiv = static_cast<int>(H / Hkv);
 
   CUtensorMap tq, tdo, tk, tv;
   if ((e = encode_tmap_bnhd(&tq, q, dtype, B, N, H, D, sq_b, sq_n, sq_h, 64, q_block_size)))
     return e;
   if ((e = encode_tmap_bnhd(&tdo, dout, dtype, B, N, H, D, sdo_b, sdo_n, sdo_h, 64, q_block_size)))
     return e;
-  if ((e = encode_tmap_bnhd(&tk, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, 128))) return e;
-  if ((e = encode_tmap_bnhd(&tv, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, 128))) return e;
+  if ((e = encode_tmap_bnhd(&tk, k, dtype, B, N, Hkv, D, sk_b, sk_n, sk_h, 64, 128))) return e;
+  if ((e = encode_tmap_bnhd(&tv, v, dtype, B, N, Hkv, D, sv_b, sv_n, sv_h, 64, 128))) return e;
   // head dim 128 with 64-row q and kv blocks: the kernel on pairs of SMs
   const char* env2 = getenv("FTK_DKV_2CTA");
   const bool long_lists = fwd_list_width <= 0 || 4 * static_cast<int64_t>(fwd_list_width) >= M;

@@ -127,8 +127,10 @@ sparse_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tm_q,
     if (lane == 0 && n > 0) {
       mbar_expect_tx(bar_kv, 2 * ROW_TILE_BYTES);
       for (int c = 0; c < NCH; c++) {
-        tma_load_4d(smem_u32(sK) + c * 128 * 128, &tm_k, bar_kv, c * 64, h_idx, tile_tok0, b_idx);
-        tma_load_4d(smem_u32(sV) + c * 128 * 128, &tm_v, bar_kv, c * 64, h_idx, tile_tok0, b_idx);
+        tma_load_4d(smem_u32(sK) + c * 128 * 128, &tm_k, bar_kv, c * 64, h_idx / p.kv_hdiv,
+                    tile_tok0, b_idx);
+        tma_load_4d(smem_u32(sV) + c * 128 * 128, &tm_v, bar_kv, c * 64, h_idx / p.kv_hdiv,
+                    tile_tok0, b_idx);
       }
       const int dcol = 64 * static_cast<int>(rank), rsub = 32 * static_cast<int>(rank);
       for (int i = 0; i < n; i++) {

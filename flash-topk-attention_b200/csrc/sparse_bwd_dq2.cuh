@@ -111,6 +111,7 @@ sparse_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q,
         tma_load_4d(smem_u32(sDO) + c * 128 * 128, &tm_do, bar_q, c * 64, h_idx, tile_row0, b_idx);
       }
       const int dcol = 64 * static_cast<int>(rank), rsub = 32 * static_cast<int>(rank);
+      const int hk = h_idx / p.kv_hdiv;
       for (int i = 0; i < n; i++) {
         const int s = i % DQ2_STAGES;
         if (!mbar_wait(bar_kvempty(s), ((i / DQ2_STAGES) & 1) ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
@@ -118,11 +119,11 @@ sparse_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint32_t base = smem_u32(sKV) + s * STAGE;
         mbar_expect_tx(bar_kvfull(s), STAGE);
         for (int c = 0; c < NCH; c++) {
-          tma_load_4d(base + c * 4096, &tm_k32, bar_kvfull(s), c * 64, h_idx, tok0 + rsub, b_idx);
-          tma_load_4d(base + OFF_VROW + c * 4096, &tm_v32, bar_kvfull(s), c * 64, h_idx,
-                      tok0 + rsub, b_idx);
+          tma_load_4d(base + c * 4096, &tm_k32, bar_kvfull(s), c * 64, hk, tok0 + rsub, b_idx);
+          tma_load_4d(base + OFF_VROW + c * 4096, &tm_v32, bar_kvfull(s), c * 64, hk, tok0 + rsub,
+                      b_idx);
         }
-        tma_load_4d(base + OFF_KCOL, &tm_k, bar_kvfull(s), dcol, h_idx, tok0, b_idx);
+        tma_load_4d(base + OFF_KCOL, &tm_k, bar_kvfull(s), dcol, hk, tok0, b_idx);
       }
     }
   } else if (warp == 1 && rank == 1) {

@@ -53,6 +53,7 @@ struct FwdParams {
   int64_t so_b, so_n, so_h;
   float* lse;
   int* status;
+  int kv_hdiv;          // query heads per kv head (grouped-query attention), 1 otherwise
   int* redo_out;        // pipelined kernel: one word per CTA, 1 = redo with the exact kernel
   const int* redo_in;   // exact kernel: when set, CTAs whose word is 0 return at once
 };
@@ -139,10 +140,11 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const uint32_t base = smem_u32(sKV) + s * stage_bytes;
         mbar_expect_tx(bar_kvfull(s), stage_bytes);
         for (int c = 0; c < NCH; c++)
-          tma_load_4d(base + c * kv_chunk_bytes, &tm_k, bar_kvfull(s), c * 64, h_idx, tok0, b_idx);
+          tma_load_4d(base + c * kv_chunk_bytes, &tm_k, bar_kvfull(s), c * 64, h_idx / p.kv_hdiv,
+                      tok0, b_idx);
         for (int c = 0; c < NCH; c++)
-          tma_load_4d(base + (NCH + c) * kv_chunk_bytes, &tm_v, bar_kvfull(s), c * 64, h_idx, tok0,
-                      b_idx);
+          tma_load_4d(base + (NCH + c) * kv_chunk_bytes, &tm_v, bar_kvfull(s), c * 64,
+                      h_idx / p.kv_hdiv, tok0, b_idx);
       }
     }
   } else if (warp == 1) {
@@ -499,7 +501,7 @@ extern "C" size_t ftk_sparse_fwd_workspace(int64_t B, int64_t H, int QM, int q_b
 }
 
 extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int dtype, int64_t B,
-                              int64_t H, int64_t N, int64_t D, int64_t sq_b, int64_t sq_n,
+                              int64_t H, int64_t Hkv, int64_t N, int64_t D, int64_t sq_b, int64_t sq_n,
                               int64_t sq_h, int64_t sk_b, int64_t sk_n, int64_t sk_h, int64_t sv_b,
                               int64_t sv_n, int64_t sv_h, const int32_t* merged_idx, int QM, int W,
                               int q_block_size, int kv_block_size, int q_pad_head, int kv_pad_head,
@@ -509,6 +511,8 @@ extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int d
   if (!q || !k || !v || !merged_idx || !o || !lse) return FTK_ERR_BAD_ARG;
   if (B <= 0 || H <= 0 || N <= 0 || QM <= 0 || W <= 0) return FTK_ERR_BAD_ARG;
   if (dtype != FTK_DTYPE_F16 && dtype != FTK_DTYPE_BF16) return FTK_ERR_BAD_ARG;
+  if (Hkv <= 0) Hkv = H;
+  if (H % Hkv != 0) return FTK_ERR_BAD_ARG;
   if (q_block_size <= 0 || kv_block_size <= 0) return FTK_ERR_BAD_ARG;
   if (q_pad_head < 0 || q_pad_head >= q_block_size || kv_pad_head < 0 ||
       kv_pad_head >= kv_block_size)
@@ -543,13 +547,14 @@ extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int d
   p.so_h = so_h;
   p.lse = lse;
   p.status = status;
+  p.kv_hdiv = static_cast<int>(H / Hkv);
 
   CUtensorMap tq, tk, tv;
   int e = encode_tmap_bnhd(&tq, q, dtype, B, N, H, D, sq_b, sq_n, sq_h, 64, 128);
   if (e) return e;
-  e = encode_tmap_bnhd(&tk, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, kv_block_size);
+  e = encode_tmap_bnhd(&tk, k, dtype, B, N, Hkv, D, sk_b, sk_n, sk_h, 64, kv_block_size);
   if (e) return e;
-  e = encode_tmap_bnhd(&tv, v, dtype, B, N, H, D, sv_b, sv_n, sv_h, 64, kv_block_size);
+  e = encode_tmap_bnhd(&tv, v, dtype, B, N, Hkv, D, sv_b, sv_n, sv_h, 64, kv_block_size);
   if (e) return e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // 64-row kv blocks, q blocks of 64 or 32 rows and a workspace: the
@@ -568,7 +573,7 @@ extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int d
         !(env2 && env2[0] == '0')) {
       // head dim 128: the same kernel on pairs of SMs
       CUtensorMap tk32;
-      e = encode_tmap_bnhd(&tk32, k, dtype, B, N, H, D, sk_b, sk_n, sk_h, 64, 32);
+      e = encode_tmap_bnhd(&tk32, k, dtype, B, N, Hkv, D, sk_b, sk_n, sk_h, 64, 32);
       if (e) return e;
       const size_t smem2 = 1024 + 2 * 128 * 128 + static_cast<size_t>(FP2_KST + FP2_VST) * 8192;
       dim3 grid2(2 * ((QM + 3) / 4), static_cast<unsigned>(B * H));

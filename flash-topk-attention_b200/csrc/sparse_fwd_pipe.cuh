@@ -172,14 +172,15 @@ sparse_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint32_t kb = smem_u32(sK) + sk * TILE;
         mbar_expect_tx(bar_kfull(sk), TILE);
         for (int c = 0; c < NCH; c++)
-          tma_load_4d(kb + c * CHUNK, &tm_k, bar_kfull(sk), c * 64, h_idx, tok0, b_idx);
+          tma_load_4d(kb + c * CHUNK, &tm_k, bar_kfull(sk), c * 64, h_idx / p.kv_hdiv, tok0, b_idx);
         if (!pro) {
           const int i = j - npro, sv = i % FP_VST;
           if (!mbar_wait(bar_vempty(sv), ((i / FP_VST) & 1) ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
           const uint32_t vb = smem_u32(sV) + sv * TILE;
           mbar_expect_tx(bar_vfull(sv), TILE);
           for (int c = 0; c < NCH; c++)
-            tma_load_4d(vb + c * CHUNK, &tm_v, bar_vfull(sv), c * 64, h_idx, tok0, b_idx);
+            tma_load_4d(vb + c * CHUNK, &tm_v, bar_vfull(sv), c * 64, h_idx / p.kv_hdiv, tok0,
+                        b_idx);
         }
       }
     }

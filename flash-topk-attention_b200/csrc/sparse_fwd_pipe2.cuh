@@ -161,12 +161,14 @@ sparse_fwd_pipe2_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint32_t kb = smem_u32(sK) + sk * TILE;
         mbar_expect_tx(bar_kfull(sk), TILE);
         for (int c = 0; c < NCH; c++)
-          tma_load_4d(kb + c * 4096, &tm_k32, bar_kfull(sk), c * 64, h_idx, tok0 + rsub, b_idx);
+          tma_load_4d(kb + c * 4096, &tm_k32, bar_kfull(sk), c * 64, h_idx / p.kv_hdiv,
+                      tok0 + rsub, b_idx);
         if (!pro) {
           const int i = j - npro, sv = i % FP2_VST;
           if (!mbar_wait(bar_vempty(sv), ((i / FP2_VST) & 1) ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
           mbar_expect_tx(bar_vfull(sv), TILE);
-          tma_load_4d(smem_u32(sV) + sv * TILE, &tm_v, bar_vfull(sv), dcol, h_idx, tok0, b_idx);
+          tma_load_4d(smem_u32(sV) + sv * TILE, &tm_v, bar_vfull(sv), dcol, h_idx / p.kv_hdiv,
+                      tok0, b_idx);
         }
       }
     }

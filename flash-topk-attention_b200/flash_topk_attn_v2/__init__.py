@@ -109,14 +109,15 @@ def flash_topk_attn(
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Sparse attention over merged KV block indices: (O [B,N,C], lse [B,H,N]);
     differentiable in q, k, v (reference __init__.py:136-169).  `counts` and
-    `S_MAX` are ignored, as in the reference."""
+    `S_MAX` are ignored, as in the reference.  `num_kv_heads` different from
+    `num_heads` (grouped-query attention) raises NotImplementedError in the
+    reference (__init__.py:153-156) and is supported here: k and v are then
+    [B, N, num_kv_heads * D]."""
     del counts, S_MAX
-    if num_kv_heads is not None and num_kv_heads != num_heads:
-        raise NotImplementedError("GQA (num_kv_heads != num_heads) is not supported")
     return flash_sparse_attn(
         q, k, v, merged_indices,
         num_heads=num_heads, q_block_size=q_block_size, kv_block_size=kv_block_size,
-        scale=scale, q_padding=q_padding, kv_padding=kv_padding,
+        scale=scale, q_padding=q_padding, kv_padding=kv_padding, num_kv_heads=num_kv_heads,
     )
 
 

@@ -40,13 +40,13 @@ SIGNATURES = {
     "ftk_sort_by_count_workspace": (sz, [i64, i32]),
     "ftk_sort_by_count": (i32, [vp, i64, i32, vp, vp, vp, sz, vp]),
     "ftk_sparse_fwd_workspace": (sz, [i64, i64, i32, i32]),
-    "ftk_sparse_fwd": (i32, [vp, vp, vp, i32, i64, i64, i64, i64, *_STRIDES3, *_STRIDES3,
+    "ftk_sparse_fwd": (i32, [vp, vp, vp, i32, i64, i64, i64, i64, i64, *_STRIDES3, *_STRIDES3,
                              *_STRIDES3, vp, i32, i32, i32, i32, i32, i32, f32, vp, *_STRIDES3,
                              vp, vp, sz, vp, vp]),
-    "ftk_sparse_bwd_dq": (i32, [vp, vp, vp, vp, vp, i32, i64, i64, i64, i64, *_STRIDES3,
+    "ftk_sparse_bwd_dq": (i32, [vp, vp, vp, vp, vp, i32, i64, i64, i64, i64, i64, *_STRIDES3,
                                 *_STRIDES3, *_STRIDES3, *_STRIDES3, *_STRIDES3, vp, i32, i32,
                                 i32, i32, i32, i32, f32, vp, vp, vp, *_STRIDES3, vp, vp]),
-    "ftk_sparse_bwd_dkv": (i32, [vp, vp, vp, vp, i32, i64, i64, i64, i64, *_STRIDES3, *_STRIDES3,
+    "ftk_sparse_bwd_dkv": (i32, [vp, vp, vp, vp, i32, i64, i64, i64, i64, i64, *_STRIDES3, *_STRIDES3,
                                  *_STRIDES3, *_STRIDES3, vp, vp, vp, i32, i32, i32, i32, i32,
                                  i32, f32, vp, vp, vp, *_STRIDES3, vp, *_STRIDES3, i32, vp, vp]),
 }

@@ -418,14 +418,15 @@ class FlashSparseAttnFunc(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, merged_indices, num_heads, q_block_size, kv_block_size, scale,
-                q_pad_head, kv_pad_head, num_kv_blocks):
+                q_pad_head, kv_pad_head, num_kv_blocks, num_kv_heads=None):
         B, N, C = q.shape
         H = num_heads
+        Hkv = num_kv_heads or H
         D = C // H
         dev = q.device
         qq, sq_b, sq_n, sq_h = _as_bnhd(q, False, H, D)
-        kk, sk_b, sk_n, sk_h = _as_bnhd(k, False, H, D)
-        vv, sv_b, sv_n, sv_h = _as_bnhd(v, False, H, D)
+        kk, sk_b, sk_n, sk_h = _as_bnhd(k, False, Hkv, D)
+        vv, sv_b, sv_n, sv_h = _as_bnhd(v, False, Hkv, D)
         merged = merged_indices.contiguous()
         QM, W = merged.shape[2], merged.shape[3]
         o = torch.empty(B, N, C, dtype=q.dtype, device=dev)
@@ -433,7 +434,7 @@ class FlashSparseAttnFunc(torch.autograd.Function):
         ws_bytes = int(lib.ftk_sparse_fwd_workspace(B, H, QM, q_block_size))
         ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
         _call("ftk_sparse_fwd", lib.ftk_sparse_fwd, 
-            ptr(qq), ptr(kk), ptr(vv), _lib.dtype_code(qq), B, H, N, D,
+            ptr(qq), ptr(kk), ptr(vv), _lib.dtype_code(qq), B, H, Hkv, N, D,
             sq_b, sq_n, sq_h, sk_b, sk_n, sk_h, sv_b, sv_n, sv_h,
             ptr(merged), QM, W, q_block_size, kv_block_size, q_pad_head, kv_pad_head,
             float(scale), ptr(o), N * C, C, D, ptr(lse), ptr(ws), ws_bytes,
@@ -444,20 +445,20 @@ class FlashSparseAttnFunc(torch.autograd.Function):
         _after(dev)
         ctx.save_for_backward(qq, kk, vv, o, lse, merged)
         ctx.meta = (H, D, q_block_size, kv_block_size, float(scale), q_pad_head, kv_pad_head,
-                    num_kv_blocks)
+                    num_kv_blocks, Hkv)
         ctx.mark_non_differentiable(lse)
         return o, lse
 
     @staticmethod
     def backward(ctx, grad_o, _grad_lse):
         qq, kk, vv, o, lse, merged = ctx.saved_tensors
-        H, D, g, kvb, scale, qph, kph, M = ctx.meta
+        H, D, g, kvb, scale, qph, kph, M, Hkv = ctx.meta
         B, N, C = qq.shape
         dev = qq.device
         do, sdo_b, sdo_n, sdo_h = _as_bnhd(grad_o.to(qq.dtype), False, H, D)
         _, sq_b, sq_n, sq_h = _as_bnhd(qq, False, H, D)
-        _, sk_b, sk_n, sk_h = _as_bnhd(kk, False, H, D)
-        _, sv_b, sv_n, sv_h = _as_bnhd(vv, False, H, D)
+        _, sk_b, sk_n, sk_h = _as_bnhd(kk, False, Hkv, D)
+        _, sv_b, sv_n, sv_h = _as_bnhd(vv, False, Hkv, D)
         QM, W = merged.shape[2], merged.shape[3]
         status = status_word(dev)
         st = stream_ptr(dev)
@@ -467,20 +468,26 @@ class FlashSparseAttnFunc(torch.autograd.Function):
         dv = torch.empty(B, N, C, dtype=qq.dtype, device=dev)
         dt = _lib.dtype_code(qq)
         _call("ftk_sparse_bwd_dq", lib.ftk_sparse_bwd_dq, 
-            ptr(qq), ptr(kk), ptr(vv), ptr(o), ptr(do), dt, B, H, N, D,
+            ptr(qq), ptr(kk), ptr(vv), ptr(o), ptr(do), dt, B, H, Hkv, N, D,
             sq_b, sq_n, sq_h, sk_b, sk_n, sk_h, sv_b, sv_n, sv_h, N * C, C, D,
             sdo_b, sdo_n, sdo_h, ptr(merged), QM, W, g, kvb, qph, kph, scale,
             ptr(lse), ptr(delta), ptr(dq), N * C, C, D, ptr(status), st)
         _count(2)
         rev, rc, skv = flash_build_reverse_indices_cuda(merged, None, M)
         _call("ftk_sparse_bwd_dkv", lib.ftk_sparse_bwd_dkv, 
-            ptr(qq), ptr(kk), ptr(vv), ptr(do), dt, B, H, N, D,
+            ptr(qq), ptr(kk), ptr(vv), ptr(do), dt, B, H, Hkv, N, D,
             sq_b, sq_n, sq_h, sk_b, sk_n, sk_h, sv_b, sv_n, sv_h, sdo_b, sdo_n, sdo_h,
             ptr(rev), ptr(rc), ptr(skv), QM, M, g, kvb, qph, kph, scale,
             ptr(lse), ptr(delta), ptr(dk), N * C, C, D, ptr(dv), N * C, C, D, W, ptr(status), st)
         _count(1)
         _after(dev)
-        return dq, dk, dv, None, None, None, None, None, None, None, None
+        if Hkv != H:
+            # the kernel wrote one dK / dV per query head: add up each group of
+            # H / Hkv heads (fp32) to get the gradient of their shared kv head
+            grp = H // Hkv
+            dk = dk.view(B, N, Hkv, grp, D).float().sum(3).to(qq.dtype).view(B, N, Hkv * D)
+            dv = dv.view(B, N, Hkv, grp, D).float().sum(3).to(qq.dtype).view(B, N, Hkv * D)
+        return dq, dk, dv, None, None, None, None, None, None, None, None, None
 
 
 def _split_large_blocks(merged, N, g, kvb, q_pad_head, kv_pad_head):
@@ -516,14 +523,17 @@ def _split_large_blocks(merged, N, g, kvb, q_pad_head, kv_pad_head):
 
 
 def flash_sparse_attn(q, k, v, merged_indices, num_heads, q_block_size, kv_block_size,
-                      scale=None, q_padding=(0, 0), kv_padding=(0, 0)):
+                      scale=None, q_padding=(0, 0), kv_padding=(0, 0), num_kv_heads=None):
     """Block-sparse attention, differentiable in q, k, v: (O [B,N,C], lse [B,H,N]).
 
     Mirrors flash_sparse_attn (flash_topk_attn_v2/sparse_attn.py:227-392)
     including its argument checks, with one extension: q and kv blocks of up to
     128 rows (multiples of 32 above 64) are accepted for forward and backward;
     the reference rejects q blocks above 64 (sparse_attn.py:279) and its
-    dK/dV kernel is only correct up to 64-row kv blocks."""
+    dK/dV kernel is only correct up to 64-row kv blocks.  `num_kv_heads`
+    (grouped-query attention, also beyond the reference): k and v are
+    [B, N, num_kv_heads * D] and query head h reads kv head
+    h // (num_heads // num_kv_heads)."""
     if q.ndim != 3:
         raise ValueError("q must be [B, N, C]")
     if q.device.type != "cuda":
@@ -538,6 +548,11 @@ def flash_sparse_attn(q, k, v, merged_indices, num_heads, q_block_size, kv_block
     D = C // H
     if C != H * D:
         raise ValueError(f"C ({C}) must be divisible by num_heads ({H})")
+    Hkv = H if num_kv_heads is None else int(num_kv_heads)
+    if Hkv <= 0 or H % Hkv != 0:
+        raise ValueError(f"num_heads ({H}) must be a multiple of num_kv_heads ({Hkv})")
+    if k.shape != (B, N, Hkv * D) or v.shape != (B, N, Hkv * D):
+        raise ValueError(f"k and v must be [B, N, num_kv_heads * D] = {(B, N, Hkv * D)}")
     if q_block_size <= 0 or q_block_size > 128:
         raise ValueError(f"q_block_size must be in (0, 128], got {q_block_size}")
     if kv_block_size <= 0:
@@ -588,8 +603,8 @@ def flash_sparse_attn(q, k, v, merged_indices, num_heads, q_block_size, kv_block
     Dk = _kernel_head_dim(D)
     if Dk != D:
         q = _pad_head_dim(q, False, H, D, Dk)
-        k = _pad_head_dim(k, False, H, D, Dk)
-        v = _pad_head_dim(v, False, H, D, Dk)
+        k = _pad_head_dim(k, False, Hkv, D, Dk)
+        v = _pad_head_dim(v, False, Hkv, D, Dk)
     num_kv_blocks = n_kv // kv_block_size
     if q_block_size > 64 or kv_block_size > 64:
         (merged_indices, q_block_size, kv_block_size, q_pad_head, kv_pad_head,
@@ -597,7 +612,7 @@ def flash_sparse_attn(q, k, v, merged_indices, num_heads, q_block_size, kv_block
             merged_indices, N, q_block_size, kv_block_size, q_pad_head, kv_pad_head)
     o, lse = FlashSparseAttnFunc.apply(
         q, k, v, merged_indices, H, q_block_size, kv_block_size, scale, q_pad_head, kv_pad_head,
-        num_kv_blocks)
+        num_kv_blocks, Hkv)
     if Dk != D:
         o = o.view(B, N, H, Dk)[..., :D].reshape(B, N, C)
     if orig_dtype == torch.float32:

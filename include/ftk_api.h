@@ -179,7 +179,9 @@ int ftk_sort_by_count(const int32_t* counts, int64_t total, int max_count,
  * csrc/sparse_attn_kernel.cu:368).  merged_idx [B*H][QM][W]; for every real
  * query row of q-block m attends to the tokens of the blocks listed in the
  * valid prefix of its row.  o in `dtype` with strides (so_*), lse fp32
- * [B*H][N] (natural log; -inf and o = 0 for an empty list).
+ * [B*H][N] (natural log; -inf and o = 0 for an empty list).  k and v carry Hkv
+ * heads (Hkv <= 0 means H; H must be a multiple): query head h reads kv head
+ * h / (H / Hkv).  The reference rejects Hkv != H (__init__.py:153-156).
  * `workspace` (ftk_sparse_fwd_workspace bytes, may be NULL) enables the
  * pipelined kernel for 64-row kv blocks and q-blocks of 64 or 32 rows (bf16 or fp16):
  * it uses one fixed reference exponent per row, and the exact running-maximum
@@ -189,7 +191,7 @@ int ftk_sort_by_count(const int32_t* counts, int64_t total, int max_count,
  * same.  At head dim 128 the pipelined kernel runs on pairs of SMs (clusters of
  * two CTAs, tcgen05 cta_group::2); FTK_FWD_2CTA=0 selects the one-CTA form. */
 size_t ftk_sparse_fwd_workspace(int64_t B, int64_t H, int QM, int q_block_size);
-int ftk_sparse_fwd(const void* q, const void* k, const void* v, int dtype, int64_t B, int64_t H,
+int ftk_sparse_fwd(const void* q, const void* k, const void* v, int dtype, int64_t B, int64_t H, int64_t Hkv,
                    int64_t N, int64_t D, int64_t sq_b, int64_t sq_n, int64_t sq_h, int64_t sk_b,
                    int64_t sk_n, int64_t sk_h, int64_t sv_b, int64_t sv_n, int64_t sv_h,
                    const int32_t* merged_idx, int QM, int W, int q_block_size, int kv_block_size,
@@ -205,7 +207,7 @@ int ftk_sparse_fwd(const void* q, const void* k, const void* v, int dtype, int64
  * CTAs, tcgen05 cta_group::2) in both backward calls; FTK_DQ_2CTA=0 and
  * FTK_DKV_2CTA=0 select the one-CTA kernels that serve every other shape. */
 int ftk_sparse_bwd_dq(const void* q, const void* k, const void* v, const void* o, const void* dout,
-                      int dtype, int64_t B, int64_t H, int64_t N, int64_t D, int64_t sq_b,
+                      int dtype, int64_t B, int64_t H, int64_t Hkv, int64_t N, int64_t D, int64_t sq_b,
                       int64_t sq_n, int64_t sq_h, int64_t sk_b, int64_t sk_n, int64_t sk_h,
                       int64_t sv_b, int64_t sv_n, int64_t sv_h, int64_t so_b, int64_t so_n,
                       int64_t so_h, int64_t sdo_b, int64_t sdo_n, int64_t sdo_h,
@@ -216,12 +218,14 @@ int ftk_sparse_bwd_dq(const void* q, const void* k, const void* v, const void* o
 
 /* Replaces sparse_attn_bwd_dkv_launch (csrc/sparse_attn_bwd_dkv.cpp:3-16,
  * csrc/sparse_attn_bwd_dkv_kernel.cu:438): dk, dv per kv block from the
- * reverse index (one writer per kv row, no atomics).  `fwd_list_width` is the
+ * reverse index (one writer per kv row, no atomics).  With Hkv < H, dk and dv are
+ * still written per QUERY head ([b][n][H][d] through the strides given): the
+ * caller sums the H / Hkv heads of a group.  `fwd_list_width` is the
  * width W of the merged_idx lists the reverse index was built from (0 if
  * unknown); it only helps to choose between the kernel on pairs of SMs (lists
  * that can cover a good part of the blocks: 4 W >= M) and the one-CTA kernel. */
 int ftk_sparse_bwd_dkv(const void* q, const void* k, const void* v, const void* dout, int dtype,
-                       int64_t B, int64_t H, int64_t N, int64_t D, int64_t sq_b, int64_t sq_n,
+                       int64_t B, int64_t H, int64_t Hkv, int64_t N, int64_t D, int64_t sq_b, int64_t sq_n,
                        int64_t sq_h, int64_t sk_b, int64_t sk_n, int64_t sk_h, int64_t sv_b,
                        int64_t sv_n, int64_t sv_h, int64_t sdo_b, int64_t sdo_n, int64_t sdo_h,
                        const int32_t* reverse_idx, const int32_t* reverse_counts,

@@ -91,8 +91,6 @@ def test_reference_exceptions_before_any_launch(ftk):
         ftk.build_qblock_topk_indices(idx, 64, q_padding=(-1, 0))
     with pytest.raises(ValueError, match=r"\[B, H, N, K\]"):
         ftk.build_qblock_topk_indices(idx[0], 64)
-    with pytest.raises(NotImplementedError, match="GQA"):
-        ftk.flash_topk_attn(x, x, x, idx, None, 1, 64, 64, num_kv_heads=2)
     with pytest.raises(ValueError, match="requires CUDA"):
         ftk.flash_topk_attn(x, x, x, idx, None, 1, 64, 64)
 

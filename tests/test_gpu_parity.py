@@ -374,6 +374,48 @@ def test_pair_kernels_agree_with_one_cta_kernels(ftk, monkeypatch):
         _close(a, b, what=f"{what}: pair vs one-CTA kernel")
 
 
+@pytest.mark.parametrize("D,g,dtype", [(128, 64, "bf16"), (64, 32, "fp16")])
+def test_grouped_query_attention(ftk, D, g, dtype):
+    """num_kv_heads < num_heads (the reference raises NotImplementedError):
+    query head h reads kv head h // group.  The oracle sees K and V repeated
+    per query head; its dK / dV are summed over each group."""
+    H, Hkv, N, kvb = 4, 2, 512, 64
+    grp = H // Hkv
+    gen = torch.Generator().manual_seed(71)
+    dt = torch.bfloat16 if dtype == "bf16" else torch.float16
+    q = (torch.randn(1, N, H * D, generator=gen)).to(dt)
+    k = (torch.randn(1, N, Hkv * D, generator=gen)).to(dt)
+    v = (torch.randn(1, N, Hkv * D, generator=gen)).to(dt)
+    do = (torch.randn(1, N, H * D, generator=gen)).to(dt)
+    QM, M = N // g, N // kvb
+    merged = _random_lists(np.random.default_rng(19), H, QM, M, 6, empty_every=9).reshape(1, H, QM, 6)
+    qg = q.cuda().requires_grad_(True)
+    kg = k.cuda().requires_grad_(True)
+    vg = v.cuda().requires_grad_(True)
+    o, lse = ftk.flash_topk_attn(qg, kg, vg, torch.from_numpy(merged).cuda(), None, H, g, kvb,
+                                 num_kv_heads=Hkv)
+    o.backward(do.cuda())
+    ftk.check_errors()
+    assert kg.grad.shape == k.shape and vg.grad.shape == v.shape
+
+    def rep(t):   # [1, N, Hkv*D] -> [1, N, H*D], kv head of query head h = h // grp
+        return t.float().view(1, N, Hkv, 1, D).expand(1, N, Hkv, grp, D).reshape(1, N, H * D).numpy()
+
+    xq, xk, xv, xdo = q.float().numpy(), rep(k), rep(v), do.float().numpy()
+    wo, wl = orc.sparse_attn_fwd(xq, xk, xv, merged, H, g, kvb)
+    _close(o.detach().float().cpu().numpy(), wo, what="O")
+    _close(lse.cpu().numpy(), wl, what="lse")
+    wq, wk, wv = orc.sparse_attn_bwd(xq, xk, xv, o.detach().float().cpu().numpy(), wl, xdo,
+                                     merged, H, g, kvb)
+    wk = wk.reshape(1, N, Hkv, grp, D).sum(3).reshape(1, N, Hkv * D)
+    wv = wv.reshape(1, N, Hkv, grp, D).sum(3).reshape(1, N, Hkv * D)
+    lax = 0.0 if dtype == "fp16" else 1e-4
+    _close(qg.grad.float().cpu().numpy(), wq, what="dQ", stragglers=lax)
+    # each query head's share is rounded to 16 bits before the group is added up
+    _close(kg.grad.float().cpu().numpy(), wk, atol=4e-3, what="dK", stragglers=lax)
+    _close(vg.grad.float().cpu().numpy(), wv, atol=4e-3, what="dV", stragglers=lax)
+
+
 @pytest.mark.parametrize("dtype,kscale", [("bf16", 30.0), ("fp16", 4.0)])
 def test_fwd_pipelined_redo_on_exponent_range(ftk, monkeypatch, dtype, kscale):
     """Later blocks beat a row's first block by more than the format allows
@@ -478,7 +520,7 @@ def test_error_codes_through_c_abi(ftk):
         ftk.flash_topk_score(x, x)                                   # num_heads missing
     with pytest.raises(ValueError):
         ftk.flash_topk_score(x, x, 1, 64, 16, (64, 0))
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError, match="multiple of num_kv_heads"):
         ftk.flash_topk_attn(x, x, x, None, None, 1, 64, 64, num_kv_heads=2)
     with pytest.raises(ValueError):
         ftk.build_qblock_topk_indices(torch.zeros(1, 1, 100, 4, dtype=torch.int32).cuda(), 64)
