@@ -475,6 +475,81 @@ qblock_merge_kernel(const int32_t* __restrict__ idx, const float* __restrict__ s
   if (tid == 0 && counts) counts[qb] = cnt_s;
 }
 
+// Exact union of a q-block's per-row picks, ascending by block id.  Replaces
+// _build_qblock_indices_kernel of the first-generation operators
+// (flash_topk_attn/attention.py:23-67: load, sort, drop repeats, compact).
+// One CTA per q-block: the picks set bits of a shared-memory bitmap (order
+// free), then each warp lists the set bits of its words behind an exclusive
+// prefix of the word popcounts.  Rows beyond `W` entries cannot occur when W
+// >= min(g * K, blocks); a longer union is cut and reported.
+constexpr int UN_THREADS = 128;
+constexpr int UN_MAX_WORDS = 2048;   // 65536 block ids
+
+__global__ void __launch_bounds__(UN_THREADS)
+qblock_union_kernel(const int32_t* __restrict__ idx, int64_t N, int K, int g, int q_pad_head,
+                    int QM, int Mtot, int W, int32_t* __restrict__ out_idx,
+                    int32_t* __restrict__ counts, int* status) {
+  __shared__ unsigned bits[UN_MAX_WORDS];
+  __shared__ int wsum[UN_THREADS / 32];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t qb = blockIdx.x;
+  const int64_t bh = qb / QM;
+  const int m = static_cast<int>(qb - bh * QM);
+  const int words = (Mtot + 31) >> 5;
+  for (int j = tid; j < words; j += UN_THREADS) bits[j] = 0u;
+  __syncthreads();
+  const int t0 = m * g - q_pad_head;
+  const int r0 = max(t0, 0);
+  const int r1 = static_cast<int>(min(static_cast<long long>(N), static_cast<long long>(t0) + g));
+  if (r1 > r0) {
+    const int64_t base = (bh * N + r0) * K;
+    const int total = (r1 - r0) * K;
+    for (int e = tid; e < total; e += UN_THREADS) {
+      const int j = idx[base + e];
+      if (j >= Mtot) {
+        if (status) atomicCAS(status, 0, FTK_DEV_BAD_INDEX);
+      } else if (j >= 0) {
+        atomicOr(&bits[j >> 5], 1u << (j & 31));
+      }
+    }
+  }
+  __syncthreads();
+  // each thread owns a contiguous run of words: ascending ids stay ascending
+  const int per = (words + UN_THREADS - 1) / UN_THREADS;
+  const int w0 = min(tid * per, words), w1 = min(w0 + per, words);
+  int mine = 0;
+  for (int j = w0; j < w1; j++) mine += __popc(bits[j]);
+  int incl = mine;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += t;
+  }
+  if (lane == 31) wsum[warp] = incl;
+  __syncthreads();
+  int before = incl - mine, total_cnt = 0;
+  for (int x = 0; x < UN_THREADS / 32; x++) {
+    if (x < warp) before += wsum[x];
+    total_cnt += wsum[x];
+  }
+  int32_t* oi = out_idx + qb * W;
+  for (int j = w0; j < w1; j++) {
+    unsigned b = bits[j];
+    while (b) {
+      const int bit = __ffs(b) - 1;
+      b &= b - 1;
+      if (before < W) oi[before] = j * 32 + bit;
+      before++;
+    }
+  }
+  const int kept = min(total_cnt, W);
+  for (int r = kept + tid; r < W; r += UN_THREADS) oi[r] = -1;
+  if (tid == 0) {
+    if (counts) counts[qb] = kept;
+    if (total_cnt > W && status) atomicCAS(status, 0, FTK_DEV_BAD_INDEX);
+  }
+}
+
 __global__ void max_index_kernel(const int32_t* __restrict__ idx, int64_t n, int32_t* result) {
   int mx = 0;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
@@ -710,6 +785,26 @@ extern "C" int ftk_qblock_merge(const int32_t* topk_idx, const float* topk_score
   qblock_merge_kernel<<<static_cast<unsigned>(BH * QM), MG_THREADS, smem, st>>>(
       topk_idx, topk_scores, N, K, q_block_size, q_pad_head, static_cast<int>(QM),
       num_score_blocks, Mp, qblock_topk, merged_idx, merged_scores, counts, status);
+  return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+}
+
+extern "C" int ftk_qblock_union(const int32_t* topk_idx, int64_t BH, int64_t N, int K,
+                                int q_block_size, int q_pad_head, int q_pad_tail,
+                                int num_score_blocks, int width, int32_t* merged_idx,
+                                int32_t* counts, int32_t* status, void* stream) {
+  if (!topk_idx || !merged_idx || BH <= 0 || N <= 0 || K <= 0) return FTK_ERR_BAD_ARG;
+  if (q_block_size <= 0 || width <= 0 || num_score_blocks <= 0) return FTK_ERR_BAD_ARG;
+  if (q_pad_head < 0 || q_pad_tail < 0 || q_pad_head >= q_block_size ||
+      q_pad_tail >= q_block_size)
+    return FTK_ERR_BAD_ARG;
+  if ((q_pad_head + N + q_pad_tail) % q_block_size != 0) return FTK_ERR_BAD_ARG;
+  if (num_score_blocks > UN_MAX_WORDS * 32) return FTK_ERR_UNSUPPORTED;
+  const int64_t QM = (q_pad_head + N + q_pad_tail) / q_block_size;
+  if (BH * QM > 0x7fffffffLL) return FTK_ERR_BAD_ARG;
+  qblock_union_kernel<<<static_cast<unsigned>(BH * QM), UN_THREADS, 0,
+                        static_cast<cudaStream_t>(stream)>>>(
+      topk_idx, N, K, q_block_size, q_pad_head, static_cast<int>(QM), num_score_blocks, width,
+      merged_idx, counts, status);
   return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
 }
 

@@ -32,6 +32,7 @@ SIGNATURES = {
                              i32, i32, i32, f32, i32, f32, vp, vp, vp, vp, sz, vp, vp]),
     "ftk_qblock_merge": (i32, [vp, vp, i64, i64, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp,
                                vp]),
+    "ftk_qblock_union": (i32, [vp, i64, i64, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp]),
     "ftk_max_index_plus1": (i32, [vp, i64, vp, vp]),
     "ftk_build_reverse_workspace": (sz, [i64, i32, i32]),
     "ftk_build_reverse": (i32, [vp, vp, i64, i32, i32, i32, vp, vp, vp, vp, sz, vp, vp]),

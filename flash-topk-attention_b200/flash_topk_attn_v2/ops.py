@@ -357,6 +357,40 @@ def flash_qblock_merge(topk_indices, topk_scores, q_block_size, qblock_topk, num
     return merged, mscores
 
 
+def flash_qblock_union(topk_indices, q_block_size, q_padding=(0, 0), num_score_blocks=None,
+                       width=None):
+    """Distinct block ids picked inside each q-block, ascending, -1 padded:
+    (merged [B, H, QM, width] int32, counts [B, H, QM] int32).
+
+    The exact-union merge of the first-generation operators
+    (flash_topk_attn/attention.py:70-138).  `width` defaults to the
+    reference's next_pow2(q_block_size * K); `num_score_blocks` bounds the ids
+    (default: read back from the indices, one host round trip)."""
+    if topk_indices.ndim != 4:
+        raise ValueError("topk_indices must be [B, H, N, K]")
+    if topk_indices.device.type != "cuda":
+        raise ValueError("flash_qblock_union requires CUDA tensors")
+    B, H, N, K = topk_indices.shape
+    qh, qt = q_padding
+    QM = (qh + N + qt) // q_block_size
+    dev = topk_indices.device
+    idx = topk_indices.to(torch.int32).contiguous()
+    if num_score_blocks is None:
+        num_score_blocks = max(int(idx.max().item()) + 1, 1)
+    if num_score_blocks > 65536:
+        raise NotImplementedError(f"num_score_blocks={num_score_blocks} exceeds 65536")
+    if width is None:
+        width = _next_pow2(q_block_size * K)
+    merged = torch.empty(B, H, QM, width, dtype=torch.int32, device=dev)
+    counts = torch.empty(B, H, QM, dtype=torch.int32, device=dev)
+    _call("ftk_qblock_union", lib.ftk_qblock_union,
+          ptr(idx), B * H, N, K, q_block_size, qh, qt, num_score_blocks, width, ptr(merged),
+          ptr(counts), ptr(status_word(dev)), stream_ptr(dev))
+    _count(1)
+    _after(dev)
+    return merged, counts
+
+
 # --------------------------------------------------------------------------
 # reverse index / count sort
 # --------------------------------------------------------------------------

@@ -124,6 +124,18 @@ int ftk_qblock_merge(const int32_t* topk_idx, const float* topk_scores, int64_t 
                      int num_score_blocks, int qblock_topk, int32_t* merged_idx,
                      float* merged_scores, int32_t* counts, int32_t* status, void* stream);
 
+/* Exact union, ascending by block id: replaces the first-generation
+ * build_qblock_topk_indices (flash_topk_attn/attention.py:70-138 and its
+ * kernel :23-67).  topk_idx [BH][N][K] (-1 = empty slot); output rows
+ * [BH][QM][width]: the distinct ids picked by the q-block's real rows in
+ * ascending order, then -1; counts [BH][QM].  width >= min(q_block_size * K,
+ * num_score_blocks) always holds the whole union (the reference uses
+ * next_pow2(q_block_size * K)); a longer union is cut at `width` and reported
+ * through `status`.  num_score_blocks <= 65536. */
+int ftk_qblock_union(const int32_t* topk_idx, int64_t BH, int64_t N, int K, int q_block_size,
+                     int q_pad_head, int q_pad_tail, int num_score_blocks, int width,
+                     int32_t* merged_idx, int32_t* counts, int32_t* status, void* stream);
+
 /* Largest valid id + 1 over an int32 array (device result, int32, >= 1):
  * the `indices.max().item() + 1` of flash_topk_attn_v2/__init__.py:101-105
  * without the host round trip. */

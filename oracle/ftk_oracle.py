@@ -43,6 +43,9 @@ __all__ = [
     "build_reverse_indices",
     "sort_by_count",
     "classify_topk_mismatches",
+    "v1_topk_score",
+    "v1_qblock_union",
+    "v1_topk_attn",
 ]
 
 
@@ -546,3 +549,103 @@ def classify_topk_mismatches(
         "hard": hard,
         "hard_examples": hard_examples,
     }
+
+
+# --------------------------------------------------------------------------
+# first-generation operators (package flash_topk_attn of the reference)
+# --------------------------------------------------------------------------
+def v1_topk_score(
+    q, k, v=None, num_heads=None, block_size=64, topk=16, padding=(0, 0),
+    score_only=False, work=np.float64,
+):
+    """Top-k blocks per query without a threshold, plus the dense attention
+    output unless `score_only`.
+
+    Restates `_flash_topk_score_naive` (flash_topk_attn/scoring.py:1360-1469):
+    block scores are softmax sums when there is no padding and sums divided by
+    the block's real-token count when there is (:1448-1459); the k best are
+    returned best first (ties: lower block id, where the reference's
+    torch.topk leaves the order open).  Returns (idx int32, scores[, o]) with
+    idx / scores [B,H,N,min(topk,M)] and o [B,N,C] unrounded; also the full
+    score table as the last element for tie arbitration.
+    """
+    if not score_only and v is None:
+        raise ValueError("v is required when score_only=False")
+    b, n, c = q.shape
+    h = num_heads
+    m, starts, ends, valid = block_geometry(n, block_size, padding)
+    if topk > m:
+        raise ValueError(f"topk ({topk}) > num_blocks ({m})")
+    sums = block_score(q, k, h, block_size, padding, work=work)
+    if tuple(padding) == (0, 0):
+        table = sums
+    else:
+        table = sums / np.maximum(valid, 1).astype(work)
+        table[..., valid == 0] = 0
+    kk = min(topk, m)
+    order = np.argsort(-table, axis=-1, kind="stable")[..., :kk]
+    scores = np.take_along_axis(table, order, axis=-1)
+    idx = order.astype(np.int32)
+    if score_only:
+        return idx, scores, table
+    d = c // h
+    qq = _split_heads(q, h).astype(work)
+    kh = _split_heads(k, h).astype(work)
+    vv = _split_heads(v, h).astype(work)
+    o = np.zeros((b, h, n, d), dtype=work)
+    for bi in range(b):
+        for hi in range(h):
+            s = (qq[bi, hi] * work(d ** -0.5)) @ kh[bi, hi].T
+            s -= s.max(axis=1, keepdims=True)
+            np.exp(s, out=s)
+            s /= s.sum(axis=1, keepdims=True)
+            o[bi, hi] = s @ vv[bi, hi]
+    return o.transpose(0, 2, 1, 3).reshape(b, n, c), idx, scores, table
+
+
+def v1_qblock_union(topk_indices, q_block_size, q_padding=(0, 0)):
+    """Distinct block ids of each q-block's rows, ascending, -1 padded to
+    S_MAX = next_pow2(q_block_size * K): (merged [B,H,QM,S_MAX] int32, counts
+    [B,H,QM] int32, S_MAX).  Restates build_qblock_topk_indices and its
+    load / sort / drop-repeats / compact kernel
+    (flash_topk_attn/attention.py:23-67, :70-138)."""
+    b, h, n, kq = topk_indices.shape
+    qh_, qt_ = q_padding
+    if qh_ >= q_block_size or qt_ >= q_block_size:
+        raise ValueError("q padding must be smaller than q_block_size")
+    if (qh_ + n + qt_) % q_block_size != 0:
+        raise ValueError("q padding does not tile")
+    qm = (qh_ + n + qt_) // q_block_size
+    raw = q_block_size * kq
+    s_max = 1 if raw <= 1 else 1 << (raw - 1).bit_length()
+    merged = np.full((b, h, qm, s_max), -1, dtype=np.int32)
+    counts = np.zeros((b, h, qm), dtype=np.int32)
+    for bi in range(b):
+        for hi in range(h):
+            for m in range(qm):
+                r0 = max(0, m * q_block_size - qh_)
+                r1 = min(n, (m + 1) * q_block_size - qh_)
+                if r0 >= r1:
+                    continue
+                ids = np.unique(topk_indices[bi, hi, r0:r1])
+                ids = ids[ids >= 0]
+                merged[bi, hi, m, : ids.size] = ids
+                counts[bi, hi, m] = ids.size
+    return merged, counts, s_max
+
+
+def v1_topk_attn(
+    q, k, v, merged_indices, counts, num_heads, q_block_size, kv_block_size,
+    scale=None, kv_padding=(0, 0), q_padding=(0, 0), work=np.float64,
+):
+    """Attention over the first counts[b,h,m] listed blocks of each q-block;
+    the index tensor may carry one head shared by all heads.  Restates
+    `_flash_topk_attn_naive` (flash_topk_attn/attention.py:571-647) on top of
+    sparse_attn_fwd: (O [B,N,C] unrounded, lse [B,H,N])."""
+    mi = np.array(merged_indices, dtype=np.int64, copy=True)
+    slot = np.arange(mi.shape[-1])
+    mi[slot >= np.asarray(counts)[..., None]] = -1
+    if mi.shape[1] == 1 and num_heads > 1:
+        mi = np.repeat(mi, num_heads, axis=1)
+    return sparse_attn_fwd(q, k, v, mi, num_heads, q_block_size, kv_block_size, scale,
+                           q_padding, kv_padding, work=work)

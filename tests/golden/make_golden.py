@@ -99,6 +99,54 @@ def run_case(name: str, ref) -> dict:
     return out
 
 
+V1_CASES = ("tiny_fp16", "ragged_bf16")
+
+
+def run_case_v1(name: str, score_naive, attn_naive) -> dict:
+    """Outputs of the first-generation package's dense twins
+    (flash_topk_attn/scoring.py `_flash_topk_score_naive`,
+    flash_topk_attn/attention.py `_flash_topk_attn_naive`) on the same seeded
+    inputs.  The exact-union merge has no pure-PyTorch twin in the reference
+    (only a Triton kernel), so the lists fed to the attention twin are built
+    here with torch.unique, which is that kernel's definition."""
+    cfg = cases.GOLDEN_CASES[name]
+    t = cases.make_inputs(cfg)
+    q, k, v = t["q"], t["k"], t["v"]
+    H, b, pad = cfg["H"], cfg["score_block_size"], tuple(cfg["padding"])
+    o, idx, scores = score_naive(q, k, v, num_heads=H, block_size=b, topk=cfg["topk"],
+                                 padding=pad, score_only=False)
+    g, qpad = cfg["q_block_size"], tuple(cfg["q_padding"])
+    kvb, kvpad = cfg["kv_block_size"], tuple(cfg["kv_padding"])
+    B, _, N, K = idx.shape
+    QM = (qpad[0] + N + qpad[1]) // g
+    width = 1 << (g * K - 1).bit_length()
+    merged = torch.full((B, H, QM, width), -1, dtype=torch.int32)
+    counts = torch.zeros(B, H, QM, dtype=torch.int32)
+    for bi in range(B):
+        for hi in range(H):
+            for m in range(QM):
+                r0, r1 = max(0, m * g - qpad[0]), min(N, (m + 1) * g - qpad[0])
+                if r0 < r1:
+                    ids = torch.unique(idx[bi, hi, r0:r1])
+                    merged[bi, hi, m, : ids.numel()] = ids.int()
+                    counts[bi, hi, m] = ids.numel()
+    ao, alse = attn_naive(q, k, v, merged, counts, H, g, kvb, None, kvpad, qpad)
+    # one index head shared by all heads, and a count that hides the last entry
+    shared, shared_counts = merged[:, :1].contiguous(), (counts[:, :1] - 1).clamp(min=0)
+    so, slse = attn_naive(q, k, v, shared, shared_counts, H, g, kvb, None, kvpad, qpad)
+    return {
+        "o_dense": o.float().numpy(),
+        "topk_idx": idx.numpy().astype(np.int16),
+        "topk_scores": scores.float().numpy(),
+        "merged": merged.numpy().astype(np.int16),
+        "counts": counts.numpy(),
+        "attn_o": ao.float().numpy(),
+        "attn_lse": alse.numpy(),
+        "shared_o": so.float().numpy(),
+        "shared_lse": slse.numpy(),
+    }
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True,
@@ -134,6 +182,16 @@ def main() -> None:
         path = os.path.join(HERE, f"{name}.npz")
         np.savez_compressed(path, **out)
         print(name, {k: v.shape for k, v in out.items()},
+              f"{os.path.getsize(path) / 1024:.0f} KiB")
+
+    from flash_topk_attn.attention import _flash_topk_attn_naive
+    from flash_topk_attn.scoring import _flash_topk_score_naive
+
+    for name in V1_CASES:
+        out = run_case_v1(name, _flash_topk_score_naive, _flash_topk_attn_naive)
+        path = os.path.join(HERE, f"v1_{name}.npz")
+        np.savez_compressed(path, **out)
+        print("v1", name, {k: v.shape for k, v in out.items()},
               f"{os.path.getsize(path) / 1024:.0f} KiB")
 
 

@@ -144,3 +144,33 @@ def test_large_block_lists_split_into_half_blocks():
         assert m2.shape[2] * g2 >= qph2 + N and int(m2.max()) < mkv2
         got = token_sets(m2.numpy(), N, g2, kvb2, qph2, kph2)
         assert got == want, (N, g, kvb)
+
+
+def test_first_generation_api_names_and_signatures():
+    """The older package name keeps the reference's three signatures
+    (flash_topk_attn/__init__.py:1-4, scoring.py:1289-1299, attention.py:70-74,
+    :423-437) and refuses CPU tensors before any launch."""
+    import inspect
+    import flash_topk_attn as v1
+    assert v1.__all__ == ["flash_topk_score", "flash_topk_attn", "build_qblock_topk_indices"]
+    s = inspect.signature(v1.flash_topk_score)
+    assert list(s.parameters) == ["q", "k", "v", "num_heads", "score_block_size", "topk",
+                                  "padding", "score_only", "backend"]
+    assert s.parameters["score_only"].default is False
+    assert s.parameters["backend"].default == "triton"
+    assert list(inspect.signature(v1.build_qblock_topk_indices).parameters) == [
+        "topk_indices", "q_block_size", "q_padding"]
+    assert list(inspect.signature(v1.flash_topk_attn).parameters) == [
+        "q", "k", "v", "merged_indices", "counts", "num_heads", "q_block_size", "kv_block_size",
+        "scale", "num_kv_heads", "kv_padding", "q_padding", "S_MAX"]
+    x = torch.zeros(1, 128, 64)
+    with pytest.raises(ValueError, match="requires CUDA"):
+        v1.flash_topk_score(x, x, x, 1, topk=2)
+    with pytest.raises(ValueError, match="topk"):
+        v1.flash_topk_score(x, x, x, 1)
+    with pytest.raises(ValueError, match="unsupported backend"):
+        v1.flash_topk_score(x, x, x, 1, backend="cuda")
+    with pytest.raises(ValueError, match="requires CUDA"):
+        v1.build_qblock_topk_indices(torch.zeros(1, 1, 128, 2, dtype=torch.int32), 32)
+    with pytest.raises(AssertionError):
+        v1.flash_topk_attn(x, x, x, None, None, 1, 32, 64)

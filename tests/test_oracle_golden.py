@@ -178,3 +178,53 @@ def test_merge_edge_cases():
     assert counts.tolist() == [[[2, 0]]]
     with pytest.raises(ValueError):
         orc.build_qblock_topk_indices(idx, 3)
+
+
+V1_GOLDEN = ("tiny_fp16", "ragged_bf16")
+
+
+@pytest.mark.parametrize("name", V1_GOLDEN)
+def test_first_generation_operators(name):
+    """oracle v1_* functions against the reference's first-generation dense
+    twins (golden files v1_<case>.npz)."""
+    cfg = cases.GOLDEN_CASES[name]
+    gold = _load(f"v1_{name}")
+    x = _np_inputs(cfg)
+    H, b, pad = cfg["H"], cfg["score_block_size"], tuple(cfg["padding"])
+    B, N = cfg["B"], cfg["N"]
+    o, idx, scores, table = orc.v1_topk_score(
+        x["q"], x["k"], x["v"], H, b, cfg["topk"], pad, score_only=False)
+    # the dense twin returns o as [B, H, N, D] for [B, N, C] input, rounded to
+    # the input dtype
+    o_bhnd = o.reshape(B, N, H, -1).transpose(0, 2, 1, 3)
+    _close(o_bhnd, gold["o_dense"], atol=4e-3)
+    rep = orc.classify_topk_mismatches(idx, gold["topk_idx"].astype(np.int32), table)
+    assert rep["hard"] == 0, rep
+    _close(scores, gold["topk_scores"], atol=1e-6, rtol=2e-5)
+    i2, s2, _ = orc.v1_topk_score(x["q"], x["k"], None, H, b, cfg["topk"], pad, score_only=True)
+    assert (i2 == idx).all() and (s2 == scores).all()
+
+    g, qpad = cfg["q_block_size"], tuple(cfg["q_padding"])
+    kvb, kvpad = cfg["kv_block_size"], tuple(cfg["kv_padding"])
+    merged, counts, width = orc.v1_qblock_union(gold["topk_idx"].astype(np.int32), g, qpad)
+    assert width == gold["merged"].shape[-1]
+    assert (merged == gold["merged"]).all() and (counts == gold["counts"]).all()
+    ao, alse = orc.v1_topk_attn(x["q"], x["k"], x["v"], merged, counts, H, g, kvb, None,
+                                kvpad, qpad)
+    _close(ao, gold["attn_o"], atol=4e-3)
+    _close(alse, gold["attn_lse"], atol=1e-4, rtol=1e-5)
+    so, slse = orc.v1_topk_attn(x["q"], x["k"], x["v"], merged[:, :1],
+                                np.maximum(counts[:, :1] - 1, 0), H, g, kvb, None, kvpad, qpad)
+    _close(so, gold["shared_o"], atol=4e-3)
+    _close(slse, gold["shared_lse"], atol=1e-4, rtol=1e-5)
+
+
+def test_first_generation_union_edges():
+    idx = np.full((1, 1, 8, 2), -1, dtype=np.int32)
+    idx[0, 0, 0] = (5, 5)
+    idx[0, 0, 1] = (3, 70000 % 4096)
+    idx[0, 0, 5] = (0, -1)
+    merged, counts, width = orc.v1_qblock_union(idx, 4, (2, 2))
+    assert width == 8 and merged.shape == (1, 1, 3, 8)
+    assert merged[0, 0, 0, :3].tolist() == [3, 5, 368] and counts[0, 0].tolist() == [3, 1, 0]
+    assert merged[0, 0, 2].tolist() == [-1] * 8 and merged[0, 0, 1, :2].tolist() == [0, -1]
