@@ -504,13 +504,35 @@ qblock_union_kernel(const int32_t* __restrict__ idx, int64_t N, int K, int g, in
   if (r1 > r0) {
     const int64_t base = (bh * N + r0) * K;
     const int total = (r1 - r0) * K;
-    for (int e = tid; e < total; e += UN_THREADS) {
-      const int j = idx[base + e];
+    auto mark = [&](int j) {
       if (j >= Mtot) {
         if (status) atomicCAS(status, 0, FTK_DEV_BAD_INDEX);
       } else if (j >= 0) {
         atomicOr(&bits[j >> 5], 1u << (j & 31));
       }
+    };
+    const int32_t* src = idx + base;
+    if ((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (total & 3) == 0) {
+      // 16-byte loads, four in flight per thread
+      const int4* src4 = reinterpret_cast<const int4*>(src);
+      const int quads = total >> 2;
+      for (int e0 = 0; e0 < quads; e0 += 4 * UN_THREADS) {
+        int4 t[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          const int e = e0 + u * UN_THREADS + tid;
+          t[u] = e < quads ? __ldg(src4 + e) : make_int4(-1, -1, -1, -1);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          mark(t[u].x);
+          mark(t[u].y);
+          mark(t[u].z);
+          mark(t[u].w);
+        }
+      }
+    } else {
+      for (int e = tid; e < total; e += UN_THREADS) mark(src[e]);
     }
   }
   __syncthreads();
@@ -543,7 +565,14 @@ qblock_union_kernel(const int32_t* __restrict__ idx, int64_t N, int K, int g, in
     }
   }
   const int kept = min(total_cnt, W);
-  for (int r = kept + tid; r < W; r += UN_THREADS) oi[r] = -1;
+  if ((reinterpret_cast<uintptr_t>(oi) & 15) == 0 && (W & 3) == 0) {
+    const int a = min((kept + 3) & ~3, W);
+    if (tid < a - kept) oi[kept + tid] = -1;
+    int4* o4 = reinterpret_cast<int4*>(oi);
+    for (int r = (a >> 2) + tid; r < (W >> 2); r += UN_THREADS) o4[r] = make_int4(-1, -1, -1, -1);
+  } else {
+    for (int r = kept + tid; r < W; r += UN_THREADS) oi[r] = -1;
+  }
   if (tid == 0) {
     if (counts) counts[qb] = kept;
     if (total_cnt > W && status) atomicCAS(status, 0, FTK_DEV_BAD_INDEX);
