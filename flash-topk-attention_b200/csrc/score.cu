@@ -33,6 +33,8 @@ constexpr int SC_KT = 128;         // key rows per tile (UMMA N)
 constexpr int SC_STAGES = 4;       // K tile ring depth
 constexpr int SC_THREADS = 576;    // 2 + 2 x 8 warps
 constexpr int SC_CHUNK_BYTES = 128 * 128;  // 128 rows x 64 16-bit elements
+__host__ __device__ constexpr int score_ksplit(int d) { return d > 128 ? 2 : 1; }
+__host__ __device__ constexpr int score_stages(int d) { return d > 128 ? 2 : SC_STAGES; }
 
 struct ScoreParams {
   int N, M, D;
@@ -92,7 +94,13 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
              const ScoreParams p) {
   constexpr int NCH = D / 64;                       // 128-byte chunks per row
   constexpr int Q_BYTES = 2 * NCH * SC_CHUNK_BYTES; // 256 rows
-  constexpr int K_STAGE_BYTES = NCH * SC_CHUNK_BYTES;
+  // Head dims above 128: a K tile travels as KSPLIT slices of the head dim,
+  // one ring stage each (the 256-row Q tile leaves room for two 32 KB stages),
+  // and the tile's UMMAs accumulate over the slices.
+  constexpr int KSPLIT = score_ksplit(D);
+  constexpr int NCHS = NCH / KSPLIT;                // chunks per stage
+  constexpr int NSTG = score_stages(D);
+  constexpr int K_STAGE_BYTES = NCHS * SC_CHUNK_BYTES;
 
   if (p.mode != 0 && *p.fallback == 0) return;  // uniform: follow-up launches idle
 
@@ -163,16 +171,17 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
         for (int c = 0; c < NCH; c++)
           tma_load_4d(smem_u32(sQ) + (half * NCH + c) * SC_CHUNK_BYTES, &tm_q, bar_q, c * 64,
                       h_idx, q0 + half * 128, b_idx);
-      const uint32_t tile_bytes = static_cast<uint32_t>(p.tile_rows) * 128u * NCH;
-      for (int t = 0; t < T; t++) {
-        const int s = t % SC_STAGES;
-        const uint32_t ph = (t / SC_STAGES) & 1;
+      const uint32_t tile_bytes = static_cast<uint32_t>(p.tile_rows) * 128u * NCHS;
+      for (int u = 0; u < T * KSPLIT; u++) {
+        const int s = u % NSTG;
+        const uint32_t ph = (u / NSTG) & 1;
         if (!mbar_wait(bar_kempty(s), ph ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
+        const int t = u / KSPLIT, part = u % KSPLIT;
         const TileInfo ti = tile_info(p, t);
         mbar_expect_tx(bar_kfull(s), tile_bytes);
-        for (int c = 0; c < NCH; c++)
+        for (int c = 0; c < NCHS; c++)
           tma_load_4d(smem_u32(sK) + s * K_STAGE_BYTES + c * SC_CHUNK_BYTES, &tm_k, bar_kfull(s),
-                      c * 64, h_idx, ti.row0, b_idx);
+                      (part * NCHS + c) * 64, h_idx, ti.row0, b_idx);
       }
     }
   } else if (warp == 1) {
@@ -184,33 +193,46 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
       const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sK), 16, 1024);
       bool ok = mbar_wait(bar_q, 0, w, FTK_DEV_TIMEOUT_MMA);
       for (int t = 0; ok && t < T; t++) {
-        const int s = t % SC_STAGES;
-        const uint32_t ph = (t / SC_STAGES) & 1;
+        const int u0 = t * KSPLIT;
         const int a = t & 1;
         const uint32_t pa = (t >> 1) & 1;
         // the three barriers of a tile are waited for together (a test of a
         // completed barrier still takes ~110 cycles) and the tile's UMMAs go
         // out as one batch, so the tensor core is not left idle in between
-        const uint32_t wb[3] = {bar_kfull(s), bar_aempty(a, 0), bar_aempty(a, 1)};
-        const uint32_t wp[3] = {ph, pa ^ 1, pa ^ 1};
+        const uint32_t wb[3] = {bar_kfull(u0 % NSTG), bar_aempty(a, 0), bar_aempty(a, 1)};
+        const uint32_t wp[3] = {static_cast<uint32_t>((u0 / NSTG) & 1), pa ^ 1, pa ^ 1};
         if (!mbar_wait_all<3>(wb, wp, w, FTK_DEV_TIMEOUT_MMA)) break;
         tc_fence_after();
-        const uint64_t kdesc = desc_advance(kdesc0, s * K_STAGE_BYTES);
-        if (elect_one()) {
 #pragma unroll
-          for (int half = 0; half < 2; half++) {
-            const uint32_t d_tmem = tmem + static_cast<uint32_t>((a * 2 + half) * SC_KT);
-            const uint64_t qdesc = desc_advance(qdesc0, half * NCH * SC_CHUNK_BYTES);
-#pragma unroll
-            for (int ks = 0; ks < D / 16; ks++) {
-              const uint32_t off = (ks / 4) * SC_CHUNK_BYTES + (ks % 4) * 32;
-              umma_ss(d_tmem, desc_advance(qdesc, off), desc_advance(kdesc, off), idesc, ks > 0);
+        for (int part = 0; part < KSPLIT; part++) {
+          const int s = (u0 + part) % NSTG;
+          if (part > 0) {
+            if (!mbar_wait(bar_kfull(s), ((u0 + part) / NSTG) & 1, w, FTK_DEV_TIMEOUT_MMA)) {
+              ok = false;
+              break;
             }
-            if (half == 1) umma_commit(bar_kempty(s));  // smem stage reusable once retired
-            umma_commit(bar_afull(a, half));             // this accumulator is readable
+            tc_fence_after();
           }
+          const uint64_t kdesc = desc_advance(kdesc0, s * K_STAGE_BYTES);
+          if (elect_one()) {
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+              const uint32_t d_tmem = tmem + static_cast<uint32_t>((a * 2 + half) * SC_KT);
+              const uint64_t qdesc =
+                  desc_advance(qdesc0, (half * NCH + part * NCHS) * SC_CHUNK_BYTES);
+#pragma unroll
+              for (int ks = 0; ks < D / KSPLIT / 16; ks++) {
+                const uint32_t off = (ks / 4) * SC_CHUNK_BYTES + (ks % 4) * 32;
+                umma_ss(d_tmem, desc_advance(qdesc, off), desc_advance(kdesc, off), idesc,
+                        part > 0 || ks > 0);
+              }
+              if (half == 1) umma_commit(bar_kempty(s));  // smem stage reusable once retired
+              // this accumulator is readable
+              if (part == KSPLIT - 1) umma_commit(bar_afull(a, half));
+            }
+          }
+          __syncwarp();
         }
-        __syncwarp();
       }
     }
   } else {
@@ -406,7 +428,8 @@ template <int D>
 static int launch_score_d(const CUtensorMap& tq, const CUtensorMap& tk, ScoreParams p,
                           int64_t bh_count, cudaStream_t st) {
   constexpr int NCH = D / 64;
-  const size_t smem = 1024 + (2 * NCH + SC_STAGES * NCH) * SC_CHUNK_BYTES;
+  const size_t smem =
+      1024 + (2 * NCH + score_stages(D) * (NCH / score_ksplit(D))) * SC_CHUNK_BYTES;
   if (cudaFuncSetAttribute(score_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(smem)) != cudaSuccess)
     return FTK_ERR_CUDA;
@@ -456,7 +479,7 @@ static int run_score(const void* q, const void* k, int dtype, int64_t B, int64_t
   if (pad_head < 0 || pad_tail < 0 || pad_head >= bsz || pad_tail >= bsz) return FTK_ERR_BAD_ARG;
   if ((pad_head + N + pad_tail) % bsz != 0) return FTK_ERR_BAD_ARG;
   if (bh_begin < 0 || bh_count <= 0 || bh_begin + bh_count > B * H) return FTK_ERR_BAD_ARG;
-  if (D != 64 && D != 128) return FTK_ERR_UNSUPPORTED;
+  if (D != 64 && D != 128 && D != 256) return FTK_ERR_UNSUPPORTED;
   if (bsz % 16 != 0) return FTK_ERR_UNSUPPORTED;
   if (bh_count > 65535) return FTK_ERR_BAD_ARG;
 
@@ -494,6 +517,7 @@ static int run_score(const void* q, const void* k, int dtype, int64_t B, int64_t
   if (e) return e;
   if (cudaMemsetAsync(ws.fallback, 0, 4, st) != cudaSuccess) return FTK_ERR_CUDA;
   if (D == 64) return launch_score_d<64>(tq, tk, p, bh_count, st);
+  if (D == 256) return launch_score_d<256>(tq, tk, p, bh_count, st);
   return launch_score_d<128>(tq, tk, p, bh_count, st);
 }
 

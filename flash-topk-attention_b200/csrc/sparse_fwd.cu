@@ -56,13 +56,19 @@ struct FwdParams {
   int kv_hdiv;          // query heads per kv head (grouped-query attention), 1 otherwise
   int* redo_out;        // pipelined kernel: one word per CTA, 1 = redo with the exact kernel
   const int* redo_in;   // exact kernel: when set, CTAs whose word is 0 return at once
+  int v_off;            // first head-dim column of V / O this launch produces (head dim 256)
 };
 
-template <int D>
+// D = head dim of the Q.K^T contraction, DV = columns of V / O per launch.
+// Head dim 256 runs as two launches with DV = 128 (p.v_off = 0, 128): two
+// 256-column accumulators do not fit TMEM next to S, and Q stays in shared
+// memory.  Both launches write the same lse.
+template <int D, int DV>
 __global__ void __launch_bounds__(FW_THREADS, 1)
 sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
   constexpr int NCH = D / 64;
+  constexpr int NCV = DV / 64;
   constexpr int Q_BYTES = NCH * 128 * 128;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -83,7 +89,7 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int groups = min(p.G, p.QM - m0);
   const int tile_row0 = m0 * p.g - p.q_pad_head;
   const int kv_chunk_bytes = p.kvb * 128;
-  const int stage_bytes = 2 * NCH * kv_chunk_bytes;
+  const int stage_bytes = (NCH + NCV) * kv_chunk_bytes;
   const int NST = p.nstages;
 
   const uint32_t bar_q = smem_u32(&bars[0]);
@@ -93,7 +99,7 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   auto bar_kvempty = [&](int s) { return smem_u32(&bars[3 + FW_MAX_STAGES + s]); };
   auto bar_sfull = [&](int s) { return smem_u32(&bars[3 + 2 * FW_MAX_STAGES + s]); };
   auto bar_pfull = [&](int s) { return smem_u32(&bars[3 + 2 * FW_MAX_STAGES + 2 + s]); };
-  const bool q_tmem = p.kvb <= 64;
+  const bool q_tmem = D <= 128 && p.kvb <= 64;
   const uint32_t s_col0 = q_tmem ? 64u : 0u, s_stride = q_tmem ? 64u : 128u;
 
   if (tid == 0) {
@@ -142,8 +148,8 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         for (int c = 0; c < NCH; c++)
           tma_load_4d(base + c * kv_chunk_bytes, &tm_k, bar_kvfull(s), c * 64, h_idx / p.kv_hdiv,
                       tok0, b_idx);
-        for (int c = 0; c < NCH; c++)
-          tma_load_4d(base + (NCH + c) * kv_chunk_bytes, &tm_v, bar_kvfull(s), c * 64,
+        for (int c = 0; c < NCV; c++)
+          tma_load_4d(base + (NCH + c) * kv_chunk_bytes, &tm_v, bar_kvfull(s), p.v_off + c * 64,
                       h_idx / p.kv_hdiv, tok0, b_idx);
       }
     }
@@ -152,7 +158,7 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (n > 0) {
       // the whole warp runs this path; one elected lane issues the UMMAs
       const uint32_t idesc_s = umma_idesc(128, p.kvb, p.fmt, 0, 0);
-      const uint32_t idesc_pv = umma_idesc(128, D, p.fmt, 0, 1);
+      const uint32_t idesc_pv = umma_idesc(128, DV, p.fmt, 0, 1);
       const uint64_t qdesc0 = smem_desc_sw128(smem_u32(sQ), 16, 1024);
       const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sKV), 16, 1024);
       const uint64_t vdesc0 =
@@ -286,7 +292,7 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const bool resc = grow && l > 0.f;
         if (__any_sync(0xffffffffu, resc)) {
           const float alpha = resc ? fast_exp2(m_run - m_new) : 1.f;
-          for (int c0 = 0; c0 < D; c0 += 32) {
+          for (int c0 = 0; c0 < DV; c0 += 32) {
             uint32_t ov[32];
             tmem_ld32(o_addr + c0, ov);
             tmem_wait_ld();
@@ -348,7 +354,7 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const bool resc = grow && l > 0.f;
         if (__any_sync(0xffffffffu, resc)) {
           const float alpha = resc ? fast_exp2(m_run - m_new) : 1.f;
-          for (int c0 = 0; c0 < D; c0 += 32) {
+          for (int c0 = 0; c0 < DV; c0 += 32) {
             uint32_t ov[32];
             tmem_ld32(o_addr + c0, ov);
             tmem_wait_ld();
@@ -410,8 +416,8 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (row_valid)
         orow = static_cast<uint8_t*>(p.o) +
                2 * (static_cast<int64_t>(b_idx) * p.so_b + static_cast<int64_t>(qrow) * p.so_n +
-                    static_cast<int64_t>(h_idx) * p.so_h);
-      constexpr int HALF = D / 2;
+                    static_cast<int64_t>(h_idx) * p.so_h + p.v_off);
+      constexpr int HALF = DV / 2;
       for (int c0 = grp_w * HALF; c0 < (grp_w + 1) * HALF; c0 += 32) {
         uint32_t va[32], vb[32];
         if (n > 0) tmem_ld32(lane_addr + FW_COL_O + c0, va);
@@ -472,20 +478,25 @@ static int launch_fwd_pipe(const CUtensorMap& tq, const CUtensorMap& tk, const C
   return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
 }
 
-template <int D>
+template <int D, int DV = D>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                       FwdParams p, int64_t BH, cudaStream_t st) {
-  constexpr int NCH = D / 64;
-  const int stage_bytes = 2 * NCH * p.kvb * 128;
-  int nst = std::min(FW_MAX_STAGES, (168 * 1024) / stage_bytes);
+  constexpr int NCH = D / 64, NCV = DV / 64;
+  const int stage_bytes = (NCH + NCV) * p.kvb * 128;
+  // 227 KB per CTA less the static part (union scratch, softmax state: ~19 KB) and the Q tile
+  const int ring_bytes = (227 - 21) * 1024 - NCH * 128 * 128;
+  int nst = std::min(FW_MAX_STAGES, std::min(168 * 1024, ring_bytes) / stage_bytes);
   if (nst < 2) return FTK_ERR_UNSUPPORTED;
   p.nstages = nst;
   const size_t smem = 1024 + NCH * 128 * 128 + static_cast<size_t>(nst) * stage_bytes;
-  if (cudaFuncSetAttribute(sparse_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (cudaFuncSetAttribute(sparse_fwd_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(smem)) != cudaSuccess)
     return FTK_ERR_CUDA;
   dim3 grid((p.QM + p.G - 1) / p.G, static_cast<unsigned>(BH));
-  sparse_fwd_kernel<D><<<grid, FW_THREADS, smem, st>>>(tq, tk, tv, p);
+  for (int v_off = 0; v_off < D; v_off += DV) {
+    p.v_off = v_off;
+    sparse_fwd_kernel<D, DV><<<grid, FW_THREADS, smem, st>>>(tq, tk, tv, p);
+  }
   return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
 }
 
@@ -518,7 +529,7 @@ extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int d
       kv_pad_head >= kv_block_size)
     return FTK_ERR_BAD_ARG;
   if (static_cast<int64_t>(QM) * q_block_size < q_pad_head + N) return FTK_ERR_BAD_ARG;
-  if (D != 64 && D != 128) return FTK_ERR_UNSUPPORTED;
+  if (D != 64 && D != 128 && D != 256) return FTK_ERR_UNSUPPORTED;
   if (q_block_size > 128) return FTK_ERR_UNSUPPORTED;
   if (kv_block_size % 16 != 0 || kv_block_size > 128) return FTK_ERR_UNSUPPORTED;
   const int64_t Mkv = (kv_pad_head + N + kv_block_size - 1) / kv_block_size;
@@ -560,7 +571,7 @@ extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int d
   // 64-row kv blocks, q blocks of 64 or 32 rows and a workspace: the
   // pipelined kernel runs first and the exact kernel redoes the CTAs it flags.
   const char* env = getenv("FTK_FWD_PIPE");
-  const bool pipe = kv_block_size == 64 && (q_block_size == 64 || q_block_size == 32) && workspace &&
+  const bool pipe = D <= 128 && kv_block_size == 64 && (q_block_size == 64 || q_block_size == 32) && workspace &&
                     workspace_bytes >= ftk_sparse_fwd_workspace(B, H, QM, q_block_size) &&
                     !(env && env[0] == '0');
   if (pipe) {
@@ -603,5 +614,6 @@ extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int d
     p.redo_in = static_cast<const int*>(workspace);
   }
   if (D == 64) return launch_fwd<64>(tq, tk, tv, p, B * H, st);
+  if (D == 256) return launch_fwd<256, 128>(tq, tk, tv, p, B * H, st);
   return launch_fwd<128>(tq, tk, tv, p, B * H, st);
 }

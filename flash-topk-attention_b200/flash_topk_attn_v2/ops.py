@@ -113,7 +113,9 @@ def _kernel_head_dim(d: int) -> int:
         return 64
     if d <= 128:
         return 128
-    raise NotImplementedError(f"head dim {d} > 128 is not built yet")
+    if d <= 256:      # 160 and 256 of the reference's list (block_score_cuda.py:16) share one kernel
+        return 256
+    raise NotImplementedError(f"head dim {d} > 256 is not supported")
 
 
 def _as_bnhd(x: torch.Tensor, input_4d: bool, H: int, D: int):

@@ -1,0 +1,97 @@
+"""Head dims 160 and 256 (the top of the reference's list,
+flash_topk_attn_v2/block_score_cuda.py:16, sparse_attn.py:349-373): scoring,
+select and the attention forward against the fp64 oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import ftk_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+ATOL, RTOL = 2e-3, 1e-2
+
+
+@pytest.fixture(scope="module")
+def ftk():
+    import flash_topk_attn_v2 as m
+    return m
+
+
+def _close(got, want, what=""):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    fin = np.isfinite(want)
+    assert (np.isfinite(got) == fin).all(), what
+    err = np.abs(got[fin] - want[fin])
+    assert (err <= ATOL + RTOL * np.abs(want[fin])).all(), f"{what}: {float(err.max()):.3e}"
+
+
+@pytest.mark.parametrize("D,dtype,N,b,pad", [
+    (256, "bf16", 1024, 64, (0, 0)),
+    (256, "fp16", 600, 32, (20, 20)),      # ragged, virtual padding, three blocks per key tile
+    (160, "bf16", 512, 128, (0, 0)),       # padded to 256 on the host; scale stays 1/sqrt(160)
+    (256, "fp16", 768, 256, (0, 0)),       # score blocks spanning two key tiles
+])
+def test_scoring(ftk, D, dtype, N, b, pad):
+    H = 2
+    cfg = dict(B=1, N=N, H=H, D=D, dtype=dtype, seed=41, do_seed=42, input_scale=0.7)
+    t = cases.make_inputs(cfg)
+    x = {k: v.float().numpy() for k, v in t.items()}
+    q, k = t["q"].cuda(), t["k"].cuda()
+    want = orc.block_score(x["q"], x["k"], H, b, pad, work=np.float64)
+    got = ftk.flash_block_score(q, k, H, b, pad).cpu().numpy()
+    ftk.check_errors()
+    np.testing.assert_allclose(got, want, rtol=5e-6, atol=1e-9)
+    topk = 3
+    idx, raw, avg = ftk.flash_topk_score(q, k, H, b, topk, pad, 0.95)
+    ftk.check_errors()
+    oi, oraw, oavg, table = orc.flash_topk_score(x["q"], x["k"], H, b, topk, pad, 0.95)
+    rep = orc.classify_topk_mismatches(idx.cpu().numpy(), oi, table)
+    assert rep["hard"] == 0, rep
+    if rep["mismatched_positions"] == 0:
+        np.testing.assert_allclose(raw.cpu().numpy(), oraw, rtol=1e-5, atol=1e-9)
+        np.testing.assert_allclose(avg.cpu().numpy(), oavg, rtol=1e-5, atol=1e-9)
+
+
+@pytest.mark.parametrize("D,dtype,g,kvb,N,qpad,kvpad", [
+    (256, "bf16", 64, 64, 512, (0, 0), (0, 0)),
+    (256, "fp16", 32, 64, 300, (10, 10), (40, 44)),
+    (160, "bf16", 64, 32, 384, (0, 0), (0, 0)),
+    (256, "fp16", 128, 128, 512, (0, 0), (0, 0)),     # split into 64-row halves on the host
+    (256, "bf16", 16, 16, 256, (0, 0), (0, 0)),
+])
+def test_attention_forward(ftk, D, dtype, g, kvb, N, qpad, kvpad):
+    H = 2
+    cfg = dict(B=1, N=N, H=H, D=D, dtype=dtype, seed=43, do_seed=44)
+    t = cases.make_inputs(cfg)
+    x = {k: v.float().numpy() for k, v in t.items()}
+    QM, M = (qpad[0] + N + qpad[1]) // g, (kvpad[0] + N + kvpad[1]) // kvb
+    rng = np.random.default_rng(11)
+    W = 5
+    merged = np.full((1, H, QM, W), -1, dtype=np.int32)
+    for h in range(H):
+        for m in range(QM):
+            c = 0 if m % 5 == 4 else int(rng.integers(1, min(W, M) + 1))
+            merged[0, h, m, :c] = rng.permutation(M)[:c]
+    q, k, v = (t[n].cuda() for n in "qkv")
+    o, lse = ftk.flash_topk_attn(q, k, v, torch.from_numpy(merged).cuda(), None, H, g, kvb,
+                                 kv_padding=kvpad, q_padding=qpad)
+    ftk.check_errors()
+    assert o.shape == q.shape and o.dtype == q.dtype
+    wo, wl = orc.sparse_attn_fwd(x["q"], x["k"], x["v"], merged, H, g, kvb, None, qpad, kvpad)
+    _close(o.float().cpu().numpy(), wo, "O")
+    _close(lse.cpu().numpy(), wl, "lse")
+
+
+def test_backward_is_refused_loudly(ftk):
+    """The gradient kernels stop at head dim 128; a larger one must raise, not
+    return something."""
+    H, N, D = 1, 128, 256
+    q, k, v = (torch.randn(1, N, H * D, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+               for _ in range(3))
+    merged = torch.zeros(1, H, 2, 1, dtype=torch.int32, device="cuda")
+    o, _ = ftk.flash_topk_attn(q, k, v, merged, None, H, 64, 64)
+    with pytest.raises(NotImplementedError):
+        o.sum().backward()
