@@ -130,6 +130,7 @@ struct BwdParams {
   int64_t s0_b, s0_n, s0_h, s1_b, s1_n, s1_h;
   int* status;
   int kv_hdiv;               // query heads per kv head (grouped-query attention), 1 otherwise
+  int o_off;                 // dK/dV kernel at head dim 256: first output column of this launch
 };
 
 // ---------------------------------------------------------------------- dQ
@@ -151,6 +152,13 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
                      const __grid_constant__ CUtensorMap tm_v, const BwdParams p) {
   constexpr int NCH = D / 64;
   constexpr int ROW_TILE_BYTES = NCH * 128 * 128;
+  // Head dim 256: Q and dO (128 TMEM columns each) no longer fit next to S, dP
+  // and a 256-column dQ, so they stay in shared memory as SS operands; the
+  // rings shrink to three K and two V tiles of at most 32 rows, all behind
+  // the Q / dO tiles.  TMEM: S[2] 0/64, dP[2] 128/192, dQ 256..511.
+  constexpr bool BIG = D > 128;
+  constexpr int KST = BIG ? 3 : DQ_KST, VST = BIG ? 2 : DQ_VST;
+  constexpr uint32_t COL_S = BIG ? 0 : 128, COL_DP = BIG ? 128 : 256, COL_DQ = BIG ? 256 : 384;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -172,6 +180,7 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int kv_chunk_bytes = p.kvb * 128;
   const int tile_bytes = NCH * kv_chunk_bytes;   // one K or V tile
   auto v_slot = [&](int sv) {
+    if (BIG) return smem_u32(sK) + (KST + sv) * tile_bytes;
     return sv < 4 ? smem_u32(sV) + sv * tile_bytes
                   : smem_u32(sK) + (DQ_KST + sv - 4) * tile_bytes;
   };
@@ -233,17 +242,17 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
         tma_load_4d(smem_u32(sDO) + c * 128 * 128, &tm_do, bar_q, c * 64, h_idx, tile_row0, b_idx);
       }
       for (int i = 0; i < n; i++) {
-        const int sk = i % DQ_KST, sv = i % DQ_VST;
+        const int sk = i % KST, sv = i % VST;
         const int tok0 = static_cast<int>(un.ids[i]) * p.kvb - p.kv_pad_head;
-        if (!mbar_wait(bar_kempty(sk), ((i / DQ_KST) & 1) ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
+        if (!mbar_wait(bar_kempty(sk), ((i / KST) & 1) ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
         const uint32_t kb = smem_u32(sK) + sk * tile_bytes;
         mbar_expect_tx(bar_kfull(sk), tile_bytes);
         for (int c = 0; c < NCH; c++)
           tma_load_4d(kb + c * kv_chunk_bytes, &tm_k, bar_kfull(sk), c * 64, h_idx / p.kv_hdiv,
                       tok0, b_idx);
         // the V ring lies over the Q / dO tiles: wait until they sit in TMEM
-        if (i == 0 && !mbar_wait(bar_qt, 0, w, FTK_DEV_TIMEOUT_TMA)) break;
-        if (!mbar_wait(bar_vempty(sv), ((i / DQ_VST) & 1) ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
+        if (!BIG && i == 0 && !mbar_wait(bar_qt, 0, w, FTK_DEV_TIMEOUT_TMA)) break;
+        if (!mbar_wait(bar_vempty(sv), ((i / VST) & 1) ^ 1, w, FTK_DEV_TIMEOUT_TMA)) break;
         const uint32_t vb = v_slot(sv);
         mbar_expect_tx(bar_vfull(sv), tile_bytes);
         for (int c = 0; c < NCH; c++)
@@ -266,45 +275,58 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       auto ds_col = [&](int ks) {
         return split ? (ks >> kh_shift) * half_cols + (ks & (kh - 1)) * 8 : ks * 8;
       };
-      bool ok = mbar_wait(bar_qt, 0, w, FTK_DEV_TIMEOUT_MMA);
+      const uint64_t qdesc0 = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+      const uint64_t dodesc0 = smem_desc_sw128(smem_u32(sDO), 16, 1024);
+      bool ok = mbar_wait(BIG ? bar_q : bar_qt, 0, w, FTK_DEV_TIMEOUT_MMA);
       tc_fence_after();
       // The tensor core runs dry whenever the issuing thread waits, so every
       // barrier of a round is waited for first and the round's UMMAs (dQ of
       // tile i, then S and dP of tile i + 2) go out as one uninterrupted batch.
       auto wait_kv = [&](int i) -> bool {
-        return mbar_wait(bar_kfull(i % DQ_KST), (i / DQ_KST) & 1, w, FTK_DEV_TIMEOUT_MMA) &&
-               mbar_wait(bar_vfull(i % DQ_VST), (i / DQ_VST) & 1, w, FTK_DEV_TIMEOUT_MMA);
+        return mbar_wait(bar_kfull(i % KST), (i / KST) & 1, w, FTK_DEV_TIMEOUT_MMA) &&
+               mbar_wait(bar_vfull(i % VST), (i / VST) & 1, w, FTK_DEV_TIMEOUT_MMA);
       };
       auto mma_a = [&](int i) {   // elected lane only
-        const int sk = i % DQ_KST, sv = i % DQ_VST;
+        const int sk = i % KST, sv = i % VST;
         const uint64_t kdesc = desc_advance(kdesc0, sk * tile_bytes);
         const uint64_t vdesc = smem_desc_sw128(v_slot(sv), 16, 1024);
         const uint32_t sb = i & 1;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ks++) {
           const uint32_t koff = (ks / 4) * kv_chunk_bytes + (ks % 4) * 32;
-          umma_ts(tmem + 128 + sb * 64, tmem + ks * 8, desc_advance(kdesc, koff), idesc_a, ks > 0);
+          if (BIG)
+            umma_ss(tmem + COL_S + sb * 64,
+                    desc_advance(qdesc0, (ks / 4) * 128 * 128 + (ks % 4) * 32),
+                    desc_advance(kdesc, koff), idesc_a, ks > 0);
+          else
+            umma_ts(tmem + 128 + sb * 64, tmem + ks * 8, desc_advance(kdesc, koff), idesc_a,
+                    ks > 0);
         }
 #pragma unroll
         for (int ks = 0; ks < D / 16; ks++) {
           const uint32_t koff = (ks / 4) * kv_chunk_bytes + (ks % 4) * 32;
-          umma_ts(tmem + 256 + sb * 64, tmem + 64 + ks * 8, desc_advance(vdesc, koff), idesc_a,
-                  ks > 0);
+          if (BIG)
+            umma_ss(tmem + COL_DP + sb * 64,
+                    desc_advance(dodesc0, (ks / 4) * 128 * 128 + (ks % 4) * 32),
+                    desc_advance(vdesc, koff), idesc_a, ks > 0);
+          else
+            umma_ts(tmem + 256 + sb * 64, tmem + 64 + ks * 8, desc_advance(vdesc, koff), idesc_a,
+                    ks > 0);
         }
         umma_commit(bar_afull(sb));
         umma_commit(bar_vempty(sv));
       };
       auto mma_b = [&](int i) {   // elected lane only
-        const int s = i % DQ_KST, sb = i & 1;
+        const int s = i % KST, sb = i & 1;
         const uint64_t kmn = desc_advance(kmn0, s * tile_bytes);
         if (p.kvb == 64) {
 #pragma unroll
           for (int ks = 0; ks < 4; ks++)
-            umma_ts(tmem + 384, tmem + 256 + sb * 64 + (ks >> 1) * 32 + (ks & 1) * 8,
+            umma_ts(tmem + COL_DQ, tmem + COL_DP + sb * 64 + (ks >> 1) * 32 + (ks & 1) * 8,
                     desc_advance(kmn, ks * 2048), idesc_b, (i > 0) || (ks > 0));
         } else {
           for (int ks = 0; ks < p.kvb / 16; ks++)
-            umma_ts(tmem + 384, tmem + 256 + sb * 64 + ds_col(ks), desc_advance(kmn, ks * 2048),
+            umma_ts(tmem + COL_DQ, tmem + COL_DP + sb * 64 + ds_col(ks), desc_advance(kmn, ks * 2048),
                     idesc_b, (i > 0) || (ks > 0));
         }
         umma_commit(bar_kempty(s));
@@ -321,11 +343,11 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
         const bool more = i + 2 < n;
         const int i2 = more ? i + 2 : i;   // last rounds: the dS barrier stands in
         const uint32_t wb[3] = {bar_dsfull(i & 1),
-                                more ? bar_kfull(i2 % DQ_KST) : bar_dsfull(i & 1),
-                                more ? bar_vfull(i2 % DQ_VST) : bar_dsfull(i & 1)};
+                                more ? bar_kfull(i2 % KST) : bar_dsfull(i & 1),
+                                more ? bar_vfull(i2 % VST) : bar_dsfull(i & 1)};
         const uint32_t wp[3] = {static_cast<uint32_t>((i >> 1) & 1),
-                                static_cast<uint32_t>(more ? (i2 / DQ_KST) & 1 : (i >> 1) & 1),
-                                static_cast<uint32_t>(more ? (i2 / DQ_VST) & 1 : (i >> 1) & 1)};
+                                static_cast<uint32_t>(more ? (i2 / KST) & 1 : (i >> 1) & 1),
+                                static_cast<uint32_t>(more ? (i2 / VST) & 1 : (i >> 1) & 1)};
         if (!mbar_wait_all<3>(wb, wp, w, FTK_DEV_TIMEOUT_MMA)) break;
         tc_fence_after();
         if (elect_one()) {
@@ -351,8 +373,8 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
     const int qrow = tile_row0 + r;
     const bool row_valid = (grp < groups) && qrow >= 0 && qrow < p.N;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t s_addr = lane_addr + 128 + wg * 64;
-    const uint32_t dp_addr = lane_addr + 256 + wg * 64;
+    const uint32_t s_addr = lane_addr + COL_S + wg * 64;
+    const uint32_t dp_addr = lane_addr + COL_DP + wg * 64;
     const int cbeg = split ? colhalf * (p.kvb / 2) : 0;
     const int cend = split ? cbeg + p.kvb / 2 : (colhalf == 0 ? p.kvb : 0);
     const float c = p.scale_log2;
@@ -362,7 +384,7 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       dl = p.delta[static_cast<int64_t>(bh) * p.N + qrow];
     }
     bool ok = true;
-    if (n > 0 && colhalf == 0) {
+    if (!BIG && n > 0 && colhalf == 0) {
       // group 0 moves the Q tile, group 1 the dO tile, from (swizzled) shared
       // memory into TMEM: row r -> lane r, two 16-bit values per column
       ok = mbar_wait(bar_q, 0, w, FTK_DEV_TIMEOUT_CONSUMER);
@@ -465,7 +487,7 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       for (int c0 = (wg * 2 + colhalf) * 32; c0 < D; c0 += 128) {
         uint32_t v[32];
         if (n > 0) {
-          tmem_ld32(lane_addr + 384 + c0, v);
+          tmem_ld32(lane_addr + COL_DQ + c0, v);
           tmem_wait_ld();
         }
         if (row_valid) {
@@ -494,7 +516,10 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
 // -------------------------------------------------------------------- dK/dV
 // TMEM columns: S^T[2] 0/64 (P^T written over their first half), dP^T[2]
 // 128/192 (dS^T likewise), dV 256.., dK 384..
-template <int D>
+// D = head dim of the two contractions, DOUT = dK / dV columns per launch:
+// head dim 256 runs as two launches of 128 output columns (p.o_off = 0, 128),
+// since two 256-column accumulators do not fit TMEM next to S^T and dP^T.
+template <int D, int DOUT>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
                       const __grid_constant__ CUtensorMap tm_do,
@@ -590,7 +615,7 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
     if (n > 0) {
       // the whole warp runs this path; one elected lane issues the UMMAs
       const uint32_t idesc_a = umma_idesc(128, p.g, p.fmt, 0, 0);
-      const uint32_t idesc_b = umma_idesc(128, D, p.fmt, 0, 1);
+      const uint32_t idesc_b = umma_idesc(128, DOUT, p.fmt, 0, 1);
       const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sK), 16, 1024);
       const uint64_t vdesc0 = smem_desc_sw128(smem_u32(sV), 16, 1024);
       const uint64_t qdesc0 = smem_desc_sw128(smem_u32(sQD), 16, 1024);
@@ -628,7 +653,7 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
       };
       auto mma_b = [&](int i) {   // elected lane only
         const int s = i % NST, sb = i & 1;
-        const uint64_t qmn = desc_advance(qmn0, s * stage_bytes);
+        const uint64_t qmn = desc_advance(qmn0, s * stage_bytes + (p.o_off >> 6) * q_chunk_bytes);
         const uint64_t domn = desc_advance(qmn, NCH * q_chunk_bytes);
         if (p.g == 64) {
 #pragma unroll
@@ -780,7 +805,8 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
       if (row_valid)
         orow = base + 2 * (static_cast<int64_t>(b_idx) * sb_ + static_cast<int64_t>(tok) * sn_ +
                            static_cast<int64_t>(h_idx) * sh_);
-      for (int c0 = colhalf * 32; c0 < D; c0 += 64) {
+      if (row_valid) orow += 2 * p.o_off;
+      for (int c0 = colhalf * 32; c0 < DOUT; c0 += 64) {
         uint32_t v[32];
         if (n > 0) {
           tmem_ld32(lane_addr + 256 + which * 128 + c0, v);
@@ -824,7 +850,7 @@ static int bwd_common_checks(int dtype, int64_t B, int64_t H, int64_t N, int64_t
   if (q_pad_head < 0 || q_pad_head >= g || kv_pad_head < 0 || kv_pad_head >= kvb)
     return FTK_ERR_BAD_ARG;
   if (static_cast<int64_t>(QM) * g < q_pad_head + N) return FTK_ERR_BAD_ARG;
-  if (D != 64 && D != 128) return FTK_ERR_UNSUPPORTED;
+  if (D != 64 && D != 128 && D != 256) return FTK_ERR_UNSUPPORTED;
   if (kvb % 16 != 0 || kvb > 64) return FTK_ERR_UNSUPPORTED;
   if (B * H > 65535) return FTK_ERR_BAD_ARG;
   return FTK_OK;
@@ -924,10 +950,22 @@ extern "C" int ftk_sparse_bwd_dq(
     return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
   }
   const int nch = static_cast<int>(D / 64);
+  dim3 grid((QM + p.G - 1) / p.G, static_cast<unsigned>(B * H));
+  if (D == 256) {
+    // Q and dO resident, three K and two V tiles behind them: kv blocks of at most 32 rows
+    if (kv_block_size > 32) return FTK_ERR_UNSUPPORTED;
+    const size_t smem_big =
+        1024 + 2 * nch * 128 * 128 + static_cast<size_t>(3 + 2) * nch * kv_block_size * 128;
+    if (cudaFuncSetAttribute(sparse_bwd_dq_kernel<256>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem_big)) != cudaSuccess)
+      return FTK_ERR_CUDA;
+    sparse_bwd_dq_kernel<256><<<grid, BW_THREADS, smem_big, st>>>(tq, tdo, tk, tv, p);
+    return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+  }
   // four V slots lie over the Q / dO tiles, the rest of the V ring behind the K ring
   const size_t smem = 1024 + 2 * nch * 128 * 128 +
                       static_cast<size_t>(DQ_KST + DQ_VST - 4) * nch * kv_block_size * 128;
-  dim3 grid((QM + p.G - 1) / p.G, static_cast<unsigned>(B * H));
   if (D == 64) {
     if (cudaFuncSetAttribute(sparse_bwd_dq_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
@@ -1031,22 +1069,32 @@ extern "C" int ftk_sparse_bwd_dkv(
   }
   const int nch = static_cast<int>(D / 64);
   const int stage_bytes = 2 * nch * q_block_size * 128;
-  p.nstages = std::min(BW_MAX_STAGES, (128 * 1024) / stage_bytes);
+  // 227 KB per CTA less the static part (union scratch, lse / delta staging: ~21 KB) and the
+  // resident K / V tiles; at head dim 256 that leaves two stages of q blocks of up to 32 rows
+  const int ring_bytes = (227 - 23) * 1024 - 2 * nch * 128 * 128;
+  p.nstages = std::min(BW_MAX_STAGES, std::min(128 * 1024, ring_bytes) / stage_bytes);
   if (p.nstages < 2) return FTK_ERR_UNSUPPORTED;
   const size_t smem = 1024 + 2 * nch * 128 * 128 + static_cast<size_t>(p.nstages) * stage_bytes;
   dim3 grid((M + p.G - 1) / p.G, static_cast<unsigned>(B * H));
   if (D == 64) {
-    if (cudaFuncSetAttribute(sparse_bwd_dkv_kernel<64>,
+    if (cudaFuncSetAttribute(sparse_bwd_dkv_kernel<64, 64>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return FTK_ERR_CUDA;
-    sparse_bwd_dkv_kernel<64><<<grid, BW_THREADS, smem, st>>>(tq, tdo, tk, tv, p);
+    sparse_bwd_dkv_kernel<64, 64><<<grid, BW_THREADS, smem, st>>>(tq, tdo, tk, tv, p);
+  } else if (D == 256) {
+    if (cudaFuncSetAttribute(sparse_bwd_dkv_kernel<256, 128>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return FTK_ERR_CUDA;
+    for (p.o_off = 0; p.o_off < 256; p.o_off += 128)
+      sparse_bwd_dkv_kernel<256, 128><<<grid, BW_THREADS, smem, st>>>(tq, tdo, tk, tv, p);
   } else {
-    if (cudaFuncSetAttribute(sparse_bwd_dkv_kernel<128>,
+    if (cudaFuncSetAttribute(sparse_bwd_dkv_kernel<128, 128>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return FTK_ERR_CUDA;
-    sparse_bwd_dkv_kernel<128><<<grid, BW_THREADS, smem, st>>>(tq, tdo, tk, tv, p);
+    sparse_bwd_dkv_kernel<128, 128><<<grid, BW_THREADS, smem, st>>>(tq, tdo, tk, tv, p);
   }
   return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
 }

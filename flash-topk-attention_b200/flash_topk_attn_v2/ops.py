@@ -491,6 +491,15 @@ class FlashSparseAttnFunc(torch.autograd.Function):
         H, D, g, kvb, scale, qph, kph, M, Hkv = ctx.meta
         B, N, C = qq.shape
         dev = qq.device
+        if D > 128 and (g > 32 or kvb > 32):
+            # head dim 256: the gradient kernels hold Q / dO (dQ) or K / V (dK, dV) of 256
+            # columns in shared memory and have room for 32-row partner tiles only
+            for name, blk in (("q_block_size", g), ("kv_block_size", kvb)):
+                if blk > 32 and blk % 32 != 0:
+                    raise NotImplementedError(
+                        f"backward at head dim > 128 needs {name} <= 32 or a multiple of 32, "
+                        f"got {blk}")
+            merged, g, kvb, qph, kph, M = _split_large_blocks(merged, N, g, kvb, qph, kph, 32)
         do, sdo_b, sdo_n, sdo_h = _as_bnhd(grad_o.to(qq.dtype), False, H, D)
         _, sq_b, sq_n, sq_h = _as_bnhd(qq, False, H, D)
         _, sk_b, sk_n, sk_h = _as_bnhd(kk, False, Hkv, D)
@@ -526,8 +535,9 @@ class FlashSparseAttnFunc(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None, None, None, None, None
 
 
-def _split_large_blocks(merged, N, g, kvb, q_pad_head, kv_pad_head):
-    """Lists over blocks of 65..128 rows, restated over half-size blocks.
+def _split_large_blocks(merged, N, g, kvb, q_pad_head, kv_pad_head, limit=64):
+    """Lists over blocks of more than `limit` rows (65..128 for the default),
+    restated over half-size blocks, repeatedly if need be.
 
     The kernels work on q / kv blocks of at most 64 rows.  A block of `kvb` rows
     that starts at token j*kvb - pad is exactly the two half blocks
@@ -536,7 +546,7 @@ def _split_large_blocks(merged, N, g, kvb, q_pad_head, kv_pad_head):
     becomes those two ids (halves that lie before token 0 or at / after token N
     are dropped).  q-blocks split the same way: both halves of a q-block take
     its list.  Returns (merged', g', kvb', q_pad_head', kv_pad_head', M')."""
-    if kvb > 64:
+    while kvb > limit:
         half = kvb // 2
         s = 1 if kv_pad_head >= half else 0
         kv_pad_head -= s * half
@@ -546,7 +556,7 @@ def _split_large_blocks(merged, N, g, kvb, q_pad_head, kv_pad_head):
         keep = (merged >= 0).unsqueeze(-1) & (sub >= 0) & (start < N)
         merged = torch.where(keep, sub, torch.full_like(sub, -1)).flatten(-2)
         kvb = half
-    if g > 64:
+    while g > limit:
         half = g // 2
         s = 1 if q_pad_head >= half else 0
         q_pad_head -= s * half

@@ -144,6 +144,13 @@ def test_large_block_lists_split_into_half_blocks():
         assert m2.shape[2] * g2 >= qph2 + N and int(m2.max()) < mkv2
         got = token_sets(m2.numpy(), N, g2, kvb2, qph2, kph2)
         assert got == want, (N, g, kvb)
+        # down to 32-row blocks (gradient kernels at head dim 256), where halving allows
+        if g % 64 == 0 and kvb % 64 == 0:
+            m3, g3, kvb3, qph3, kph3, mkv3 = ops._split_large_blocks(
+                torch.from_numpy(merged), N, g, kvb, qpad[0], kpad[0], limit=32)
+            assert g3 == 32 and kvb3 == 32 and 0 <= qph3 < 32 and 0 <= kph3 < 32
+            assert m3.shape[2] * g3 >= qph3 + N and int(m3.max()) < mkv3
+            assert token_sets(m3.numpy(), N, g3, kvb3, qph3, kph3) == want, (N, g, kvb)
 
 
 def test_first_generation_api_names_and_signatures():

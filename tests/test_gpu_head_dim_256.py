@@ -1,6 +1,6 @@
 """Head dims 160 and 256 (the top of the reference's list,
 flash_topk_attn_v2/block_score_cuda.py:16, sparse_attn.py:349-373): scoring,
-select and the attention forward against the fp64 oracle."""
+select and the attention forward and backward against the fp64 oracle."""
 
 import numpy as np
 import pytest
@@ -85,13 +85,51 @@ def test_attention_forward(ftk, D, dtype, g, kvb, N, qpad, kvpad):
     _close(lse.cpu().numpy(), wl, "lse")
 
 
-def test_backward_is_refused_loudly(ftk):
-    """The gradient kernels stop at head dim 128; a larger one must raise, not
-    return something."""
-    H, N, D = 1, 128, 256
+@pytest.mark.parametrize("D,dtype,g,kvb,N,qpad,kvpad", [
+    (256, "bf16", 64, 64, 512, (0, 0), (0, 0)),       # lists restated over 32-row blocks
+    (256, "fp16", 32, 64, 300, (10, 10), (40, 44)),
+    (160, "fp16", 64, 32, 384, (0, 0), (0, 0)),
+    (256, "fp16", 128, 128, 512, (70, 58), (100, 28)),  # two rounds of halving
+    (256, "fp16", 16, 16, 256, (0, 0), (0, 0)),
+])
+def test_attention_backward(ftk, D, dtype, g, kvb, N, qpad, kvpad):
+    H = 2
+    cfg = dict(B=1, N=N, H=H, D=D, dtype=dtype, seed=45, do_seed=46)
+    t = cases.make_inputs(cfg)
+    x = {k: v.float().numpy() for k, v in t.items()}
+    QM, M = (qpad[0] + N + qpad[1]) // g, (kvpad[0] + N + kvpad[1]) // kvb
+    rng = np.random.default_rng(12)
+    W = 6
+    merged = np.full((1, H, QM, W), -1, dtype=np.int32)
+    for h in range(H):
+        for m in range(QM):
+            c = 0 if m % 5 == 4 else int(rng.integers(1, min(W, M) + 1))
+            merged[0, h, m, :c] = rng.permutation(M)[:c]
+    q, k, v = (t[n].cuda().requires_grad_(True) for n in "qkv")
+    o, lse = ftk.flash_topk_attn(q, k, v, torch.from_numpy(merged).cuda(), None, H, g, kvb,
+                                 kv_padding=kvpad, q_padding=qpad)
+    o.backward(t["do"].cuda())
+    ftk.check_errors()
+    wo, wl = orc.sparse_attn_fwd(x["q"], x["k"], x["v"], merged, H, g, kvb, None, qpad, kvpad)
+    _close(o.detach().float().cpu().numpy(), wo, "O")
+    wq, wk, wv = orc.sparse_attn_bwd(x["q"], x["k"], x["v"], o.detach().float().cpu().numpy(), wl,
+                                     x["do"], merged, H, g, kvb, None, qpad, kvpad)
+    frac = 0.0 if dtype == "fp16" else 1e-4
+    for name, got, want in (("dQ", q.grad, wq), ("dK", k.grad, wk), ("dV", v.grad, wv)):
+        got, want = got.float().cpu().numpy().astype(np.float64), np.asarray(want, np.float64)
+        err = np.abs(got - want)
+        tol = ATOL + RTOL * np.abs(want)
+        assert (err > tol).sum() <= frac * err.size and not (err > 2 * tol).any(), \
+            f"{name}: {int((err > tol).sum())} bad, max {float(err.max()):.3e}"
+
+
+def test_backward_block_sizes_that_cannot_be_halved(ftk):
+    """At head dim 256 the gradient kernels take 32-row blocks; 48 cannot be
+    restated over them and must raise, not return something."""
+    H, N, D = 1, 192, 256
     q, k, v = (torch.randn(1, N, H * D, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
                for _ in range(3))
-    merged = torch.zeros(1, H, 2, 1, dtype=torch.int32, device="cuda")
-    o, _ = ftk.flash_topk_attn(q, k, v, merged, None, H, 64, 64)
+    merged = torch.zeros(1, H, 4, 1, dtype=torch.int32, device="cuda")
+    o, _ = ftk.flash_topk_attn(q, k, v, merged, None, H, 48, 48)
     with pytest.raises(NotImplementedError):
         o.sum().backward()
