@@ -66,7 +66,7 @@ const char* ftk_error_string(int code);
  * mass of every query over every score block, block_scores[slice][n][m],
  * m < M = (pad_head + N + pad_tail) / score_block_size, rows summing to 1.
  * Logits are `scale` * q.k (the reference always uses 1/sqrt(D) of the
- * unpadded head dim, block_score_cuda.py:148).  D is 64 or 128 (the host
+ * unpadded head dim, block_score_cuda.py:148).  D is 64, 128 or 256 (the host
  * layer zero-pads other head dims up); score_block_size a multiple of 16.
  * `block_scores` points at slice bh_begin.  Workspace: ftk_block_score_workspace.
  */
@@ -201,7 +201,12 @@ int ftk_sort_by_count(const int32_t* counts, int64_t total, int max_count,
  * exponent range (none on ordinary inputs).  Without a workspace only the
  * exact kernel runs.  Setting the environment variable FTK_FWD_PIPE=0 does the
  * same.  At head dim 128 the pipelined kernel runs on pairs of SMs (clusters of
- * two CTAs, tcgen05 cta_group::2); FTK_FWD_2CTA=0 selects the one-CTA form. */
+ * two CTAs, tcgen05 cta_group::2); FTK_FWD_2CTA=0 selects the one-CTA form.
+ * Head dim 256 (D is 64, 128 or 256) runs the exact kernel as two launches of
+ * 128 output columns; ftk_sparse_bwd_dq and ftk_sparse_bwd_dkv then take kv
+ * blocks (dq) and q blocks (dkv) of at most 32 rows and return
+ * FTK_ERR_UNSUPPORTED otherwise: the host layer restates longer blocks over
+ * 32-row halves first. */
 size_t ftk_sparse_fwd_workspace(int64_t B, int64_t H, int QM, int q_block_size);
 int ftk_sparse_fwd(const void* q, const void* k, const void* v, int dtype, int64_t B, int64_t H, int64_t Hkv,
                    int64_t N, int64_t D, int64_t sq_b, int64_t sq_n, int64_t sq_h, int64_t sk_b,
