@@ -524,3 +524,43 @@ def test_error_codes_through_c_abi(ftk):
         ftk.flash_topk_attn(x, x, x, None, None, 1, 64, 64, num_kv_heads=2)
     with pytest.raises(ValueError):
         ftk.build_qblock_topk_indices(torch.zeros(1, 1, 100, 4, dtype=torch.int32).cuda(), 64)
+
+
+def test_whole_chain_replays_from_a_cuda_graph(ftk):
+    """score -> merge -> attention -> backward issues no host synchronisation
+    and keeps no state between calls, so the chain can be captured once and
+    replayed on new data: replayed results equal the eager ones bit for bit."""
+    B, N, H, D, b, g = 1, 1024, 2, 128, 64, 64
+    gen = torch.Generator().manual_seed(77)
+    data = [[torch.randn(B, N, H * D, generator=gen).bfloat16() for _ in range(4)]
+            for _ in range(2)]
+    q, k, v = (x.cuda().requires_grad_(True) for x in data[0][:3])
+    do = data[0][3].cuda()
+
+    def chain():
+        idx, raw, avg = ftk.flash_topk_score(q, k, H, b, 4, (0, 0), 0.9)
+        merged, counts, _ = ftk.build_qblock_topk_indices(idx, g, topk_scores=avg)
+        o, lse = ftk.flash_topk_attn(q, k, v, merged, counts, H, g, b)
+        gq, gk, gv = torch.autograd.grad(o, (q, k, v), do)
+        return idx, merged, o.detach(), lse, gq, gk, gv
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            chain()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = chain()
+    for tensors in (data[1], data[0]):
+        with torch.no_grad():
+            for dst, src in zip((q, k, v, do), tensors):
+                dst.copy_(src)
+        graph.replay()
+        torch.cuda.synchronize()
+        replayed = [t.clone() for t in captured]
+        eager = chain()
+        ftk.check_errors()
+        for name, a, e in zip(("idx", "merged", "o", "lse", "dq", "dk", "dv"), replayed, eager):
+            assert torch.equal(a, e), name
