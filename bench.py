@@ -164,6 +164,8 @@ def run_ours(args):
     cfg = dict(WORKLOAD)
     if args.small:
         cfg.update(N=8192, H=16, name="small")
+    if args.head_dim != cfg["D"]:
+        cfg.update(D=args.head_dim, name=f"{cfg['name']}-d{args.head_dim}")
     H, D, N, B = cfg["H"], cfg["D"], cfg["N"], cfg["B"]
     b, K, thr = cfg["score_block_size"], cfg["topk"], cfg["threshold"]
     g, kvb = cfg["q_block_size"], cfg["kv_block_size"]
@@ -334,7 +336,8 @@ def run_ours(args):
                     if d["ms"] > 0 else 0.0
         dom = max(kern, key=lambda n: kern[n]["ms"])
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+            "metric": METRIC.replace("D=128", f"D={D}").replace("N=32k", f"N={N // 1024}k"),
+            "value": value, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -468,6 +471,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--small", action="store_true", help="N=8192, H=16 (profiling-sized case)")
+    ap.add_argument("--head-dim", type=int, default=WORKLOAD["D"],
+                    help="head dim other than the headline 128 (profiling / side measurements; "
+                         "the workload name says so)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     args = ap.parse_args()
