@@ -336,7 +336,8 @@ def run_ours(args):
                     if d["ms"] > 0 else 0.0
         dom = max(kern, key=lambda n: kern[n]["ms"])
         line = {
-            "metric": METRIC.replace("D=128", f"D={D}").replace("N=32k", f"N={N // 1024}k"),
+            "metric": METRIC.replace("D=128", f"D={D}").replace("N=32k", f"N={N // 1024}k")
+            .replace("H=32", f"H={H}"),
             "value": value, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
@@ -345,7 +346,7 @@ def run_ours(args):
                        "score_block_size": b, "topk": K, "threshold": thr, "q_block_size": g,
                        "kv_block_size": kvb, "sharding": "batch x head slices, no collective",
                        "host_cores_near_gpu": near,
-                       "l2": "inputs larger than L2 (4 x 268 MB per step)",
+                       "l2": f"inputs larger than L2 (4 x {B * N * H * D * 2 // 1000000} MB per step)",
                        "candidate_pairs_per_step": P},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": bytes_in,
