@@ -265,3 +265,54 @@ def test_config5_slice_of_long_context(ftk):
             dv += p.T @ x["do"][0, r]
         _close(k.grad[0, tok, D:2 * D].float().cpu().numpy(), dk, f"dK block {j}")
         _close(v.grad[0, tok, D:2 * D].float().cpu().numpy(), dv, f"dV block {j}")
+
+
+def test_config2_first_generation_union_and_attention(ftk):
+    """The first-generation chain at B=1 N=32768 H=32 D=128 bf16: threshold-free
+    scoring, exact union, attention over the union lists.  Whole-output
+    properties (every rank filled, lists strictly ascending with a -1 tail of
+    the right length, every picked block present in its q-block's list) plus
+    sampled q-blocks against the oracle."""
+    import flash_topk_attn as v1
+    cfg = cases.BASELINE_CONFIGS[2]
+    t = cases.make_inputs(dict(cfg, B=1))
+    H, D, b, K, N = cfg["H"], cfg["D"], cfg["score_block_size"], cfg["topk"], cfg["N"]
+    q, k, v = (t[n].cuda() for n in "qkv")
+    idx, scores = v1.flash_topk_score(q, k, num_heads=H, score_block_size=b, topk=K,
+                                      score_only=True)
+    ftk.check_errors()
+    M, g = N // b, 64
+    assert idx.shape == (1, H, N, K) and int(idx.min()) >= 0 and int(idx.max()) < M
+    assert bool((scores[..., :-1] >= scores[..., 1:]).all())
+    merged, counts, width = v1.build_qblock_topk_indices(idx, g)
+    ftk.check_errors()
+    assert width == 2048 and merged.shape == (1, H, N // g, width)
+    slot = torch.arange(width, device="cuda")
+    valid = slot < counts.unsqueeze(-1)
+    assert bool(((merged >= 0) == valid).all())
+    asc = (merged[..., 1:] > merged[..., :-1]) | ~valid[..., 1:]
+    assert bool(asc.all())
+    # membership: the bitmap of each list equals the bitmap of the picks it came from
+    want_bits = torch.zeros(1, H, N // g, M, dtype=torch.bool, device="cuda")
+    want_bits.scatter_(3, idx.view(1, H, N // g, g * K).long(), True)
+    got_bits = torch.zeros(1, H, N // g, M + 1, dtype=torch.bool, device="cuda")
+    got_bits.scatter_(3, torch.where(valid, merged, torch.full_like(merged, M)).long(), True)
+    assert torch.equal(got_bits[..., :M], want_bits)
+    assert torch.equal(counts.long(), want_bits.sum(-1))
+
+    o, lse = v1.flash_topk_attn(q, k, v, merged, counts, H, g, b)
+    ftk.check_errors()
+    mh, ch = merged.cpu().numpy(), counts.cpu().numpy()
+    for h, m in ((0, 0), (13, 255), (31, 511)):
+        rows = slice(m * g, (m + 1) * g)
+        q1 = _slice_head(t["q"], 0, h, D)[:, rows]
+        k1, v1_ = _slice_head(t["k"], 0, h, D), _slice_head(t["v"], 0, h, D)
+        # one q-block on its own: pad the query side so that it is block 0 of a one-block problem
+        toks = np.concatenate([np.arange(j * b, (j + 1) * b) for j in mh[0, h, m, :ch[0, h, m]]])
+        s = (q1[0] * D ** -0.5) @ k1[0, toks].T
+        mx = s.max(1, keepdims=True)
+        p = np.exp(s - mx)
+        want_o = (p / p.sum(1, keepdims=True)) @ v1_[0, toks]
+        want_l = (mx + np.log(p.sum(1, keepdims=True)))[:, 0]
+        _close(o[0, rows, h * D:(h + 1) * D].float().cpu().numpy(), want_o, f"o h{h} m{m}")
+        _close(lse[0, h, rows].cpu().numpy(), want_l, f"lse h{h} m{m}")
