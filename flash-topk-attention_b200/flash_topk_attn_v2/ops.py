@@ -11,7 +11,6 @@ from __future__ import annotations
 
 import math
 import os
-from typing import Optional, Tuple
 
 import torch
 

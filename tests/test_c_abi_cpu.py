@@ -97,8 +97,6 @@ def test_reference_exceptions_before_any_launch(ftk):
 
 def test_no_fallback_when_library_missing(tmp_path, monkeypatch):
     """The package must refuse to import without its CUDA library."""
-    import importlib
-    import sys
     from flash_topk_attn_v2 import _lib
     monkeypatch.setattr(os.path, "exists", lambda p, _e=os.path.exists: False
                         if p == _lib.LIB_PATH else _e(p))
