@@ -130,7 +130,6 @@ struct BwdParams {
   int64_t s0_b, s0_n, s0_h, s1_b, s1_n, s1_h;
   int* status;
   int kv_hdiv;               // query heads per kv head (grouped-query attention), 1 otherwise
-  int o_off;                 // dK/dV kernel at head dim 256: first output column of this launch
 };
 
 // ---------------------------------------------------------------------- dQ
@@ -516,10 +515,12 @@ sparse_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
 // -------------------------------------------------------------------- dK/dV
 // TMEM columns: S^T[2] 0/64 (P^T written over their first half), dP^T[2]
 // 128/192 (dS^T likewise), dV 256.., dK 384..
-// D = head dim of the two contractions, DOUT = dK / dV columns per launch:
-// head dim 256 runs as two launches of 128 output columns (p.o_off = 0, 128),
-// since two 256-column accumulators do not fit TMEM next to S^T and dP^T.
-template <int D, int DOUT>
+// MODE 0 (head dims up to 128) produces dV and dK in one launch.  At head dim
+// 256 two 256-column accumulators do not fit TMEM next to S^T and dP^T, so the
+// work goes in two launches with one accumulator at columns 256..511 each:
+// MODE 1 = dV only (needs neither V nor dP^T: K alone stays resident, which
+// leaves room for four ring stages), MODE 2 = dK only.
+template <int D, int MODE>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
                       const __grid_constant__ CUtensorMap tm_do,
@@ -532,7 +533,8 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sK = smem;
   uint8_t* sV = smem + ROW_TILE_BYTES;
-  uint8_t* sQD = smem + 2 * ROW_TILE_BYTES;
+  uint8_t* sQD = smem + (MODE == 1 ? 1 : 2) * ROW_TILE_BYTES;
+  constexpr uint32_t COL_DV = 256, COL_DK = MODE == 0 ? 384 : 256;
   __shared__ UnionScratch un;
   __shared__ __align__(8) uint64_t bars[1 + 2 * BW_MAX_STAGES + 6];
   __shared__ uint32_t tmem_base_s;
@@ -591,12 +593,13 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
 
   if (warp == 0) {
     if (lane == 0 && n > 0) {
-      mbar_expect_tx(bar_kv, 2 * ROW_TILE_BYTES);
+      mbar_expect_tx(bar_kv, (MODE == 1 ? 1 : 2) * ROW_TILE_BYTES);
       for (int c = 0; c < NCH; c++) {
         tma_load_4d(smem_u32(sK) + c * 128 * 128, &tm_k, bar_kv, c * 64, h_idx / p.kv_hdiv,
                     tile_tok0, b_idx);
-        tma_load_4d(smem_u32(sV) + c * 128 * 128, &tm_v, bar_kv, c * 64, h_idx / p.kv_hdiv,
-                    tile_tok0, b_idx);
+        if (MODE != 1)
+          tma_load_4d(smem_u32(sV) + c * 128 * 128, &tm_v, bar_kv, c * 64, h_idx / p.kv_hdiv,
+                      tile_tok0, b_idx);
       }
       for (int i = 0; i < n; i++) {
         const int s = i % NST;
@@ -615,7 +618,7 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
     if (n > 0) {
       // the whole warp runs this path; one elected lane issues the UMMAs
       const uint32_t idesc_a = umma_idesc(128, p.g, p.fmt, 0, 0);
-      const uint32_t idesc_b = umma_idesc(128, DOUT, p.fmt, 0, 1);
+      const uint32_t idesc_b = umma_idesc(128, D, p.fmt, 0, 1);
       const uint64_t kdesc0 = smem_desc_sw128(smem_u32(sK), 16, 1024);
       const uint64_t vdesc0 = smem_desc_sw128(smem_u32(sV), 16, 1024);
       const uint64_t qdesc0 = smem_desc_sw128(smem_u32(sQD), 16, 1024);
@@ -642,34 +645,40 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
           umma_ss(tmem + sb * 64, desc_advance(kdesc0, aoff), desc_advance(qdesc, boff), idesc_a,
                   ks > 0);
         }
+        if (MODE != 1) {
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ks++) {
-          const uint32_t aoff = (ks / 4) * 128 * 128 + (ks % 4) * 32;
-          const uint32_t boff = (ks / 4) * q_chunk_bytes + (ks % 4) * 32;
-          umma_ss(tmem + 128 + sb * 64, desc_advance(vdesc0, aoff), desc_advance(dodesc, boff),
-                  idesc_a, ks > 0);
+          for (int ks = 0; ks < D / 16; ks++) {
+            const uint32_t aoff = (ks / 4) * 128 * 128 + (ks % 4) * 32;
+            const uint32_t boff = (ks / 4) * q_chunk_bytes + (ks % 4) * 32;
+            umma_ss(tmem + 128 + sb * 64, desc_advance(vdesc0, aoff), desc_advance(dodesc, boff),
+                    idesc_a, ks > 0);
+          }
         }
         umma_commit(bar_afull(sb));
       };
       auto mma_b = [&](int i) {   // elected lane only
         const int s = i % NST, sb = i & 1;
-        const uint64_t qmn = desc_advance(qmn0, s * stage_bytes + (p.o_off >> 6) * q_chunk_bytes);
+        const uint64_t qmn = desc_advance(qmn0, s * stage_bytes);
         const uint64_t domn = desc_advance(qmn, NCH * q_chunk_bytes);
         if (p.g == 64) {
 #pragma unroll
           for (int ks = 0; ks < 4; ks++) {
             const bool acc = (i > 0) || (ks > 0);
             const uint32_t col = sb * 64 + (ks >> 1) * 32 + (ks & 1) * 8;
-            umma_ts(tmem + 256, tmem + col, desc_advance(domn, ks * 2048), idesc_b, acc);
-            umma_ts(tmem + 384, tmem + 128 + col, desc_advance(qmn, ks * 2048), idesc_b, acc);
+            if (MODE != 2)
+              umma_ts(tmem + COL_DV, tmem + col, desc_advance(domn, ks * 2048), idesc_b, acc);
+            if (MODE != 1)
+              umma_ts(tmem + COL_DK, tmem + 128 + col, desc_advance(qmn, ks * 2048), idesc_b, acc);
           }
         } else {
           for (int ks = 0; ks < p.g / 16; ks++) {
             const bool acc = (i > 0) || (ks > 0);
-            umma_ts(tmem + 256, tmem + sb * 64 + pt_col(ks), desc_advance(domn, ks * 2048),
-                    idesc_b, acc);
-            umma_ts(tmem + 384, tmem + 128 + sb * 64 + pt_col(ks), desc_advance(qmn, ks * 2048),
-                    idesc_b, acc);
+            if (MODE != 2)
+              umma_ts(tmem + COL_DV, tmem + sb * 64 + pt_col(ks), desc_advance(domn, ks * 2048),
+                      idesc_b, acc);
+            if (MODE != 1)
+              umma_ts(tmem + COL_DK, tmem + 128 + sb * 64 + pt_col(ks),
+                      desc_advance(qmn, ks * 2048), idesc_b, acc);
           }
         }
         umma_commit(bar_qempty(s));
@@ -756,8 +765,12 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
       for (int c0 = cbeg; c0 < cend; c0 += 16) {
         uint32_t sv[16], dv[16], pp[8], pd[8];
         tmem_ld16(st_addr + c0, sv);
-        tmem_ld16(dp_addr + c0, dv);
+        if (MODE != 1) tmem_ld16(dp_addr + c0, dv);
         tmem_wait_ld();
+        if (MODE == 1) {   // no dP^T in this launch: dS^T is computed and dropped
+#pragma unroll
+          for (int x = 0; x < 16; x++) dv[x] = 0u;
+        }
         if (fast) {
           if (p.fmt == 1) pt_pairs<1>(sv, dv, l4 + (c0 >> 2), d4 + (c0 >> 2), c, pp, pd);
           else pt_pairs<0>(sv, dv, l4 + (c0 >> 2), d4 + (c0 >> 2), c, pp, pd);
@@ -783,8 +796,8 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
         }
         const int oc = cbeg + ((c0 - cbeg) >> 1);
-        tmem_st8(st_addr + oc, pp);
-        tmem_st8(dp_addr + oc, pd);
+        if (MODE != 2) tmem_st8(st_addr + oc, pp);
+        if (MODE != 1) tmem_st8(dp_addr + oc, pd);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -795,8 +808,9 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
       ok = mbar_wait(bar_final, 0, w, FTK_DEV_TIMEOUT_EPILOGUE);
     if (ok) {
       tc_fence_after();
-      // group 0 stores dV (TMEM 256..), group 1 stores dK (TMEM 384.., scaled)
-      const int which = wg;
+      // MODE 0: group 0 stores dV (TMEM 256..), group 1 stores dK (TMEM 384.., scaled);
+      // otherwise both groups share the one accumulator's columns
+      const int which = MODE == 0 ? wg : MODE - 1;
       uint8_t* base = static_cast<uint8_t*>(which == 0 ? p.out1 : p.out0);
       const int64_t sb_ = which == 0 ? p.s1_b : p.s0_b, sn_ = which == 0 ? p.s1_n : p.s0_n,
                     sh_ = which == 0 ? p.s1_h : p.s0_h;
@@ -805,11 +819,11 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
       if (row_valid)
         orow = base + 2 * (static_cast<int64_t>(b_idx) * sb_ + static_cast<int64_t>(tok) * sn_ +
                            static_cast<int64_t>(h_idx) * sh_);
-      if (row_valid) orow += 2 * p.o_off;
-      for (int c0 = colhalf * 32; c0 < DOUT; c0 += 64) {
+      const int cfirst = MODE == 0 ? colhalf * 32 : (wg * 2 + colhalf) * 32;
+      for (int c0 = cfirst; c0 < D; c0 += (MODE == 0 ? 64 : 128)) {
         uint32_t v[32];
         if (n > 0) {
-          tmem_ld32(lane_addr + 256 + which * 128 + c0, v);
+          tmem_ld32(lane_addr + (which == 0 ? COL_DV : COL_DK) + c0, v);
           tmem_wait_ld();
         }
         if (row_valid) {
@@ -1069,32 +1083,50 @@ extern "C" int ftk_sparse_bwd_dkv(
   }
   const int nch = static_cast<int>(D / 64);
   const int stage_bytes = 2 * nch * q_block_size * 128;
+  const int tile_bytes = nch * 128 * 128;          // K or V of the CTA's 128 kv rows
   // 227 KB per CTA less the static part (union scratch, lse / delta staging: ~21 KB) and the
-  // resident K / V tiles; at head dim 256 that leaves two stages of q blocks of up to 32 rows
-  const int ring_bytes = (227 - 23) * 1024 - 2 * nch * 128 * 128;
-  p.nstages = std::min(BW_MAX_STAGES, std::min(128 * 1024, ring_bytes) / stage_bytes);
-  if (p.nstages < 2) return FTK_ERR_UNSUPPORTED;
-  const size_t smem = 1024 + 2 * nch * 128 * 128 + static_cast<size_t>(p.nstages) * stage_bytes;
+  // resident tiles; at head dim 256 that leaves two stages of q blocks of up to 32 rows next to
+  // K and V, four next to K alone
+  auto stages = [&](int resident) {
+    const int ring_bytes = (227 - 23) * 1024 - resident * tile_bytes;
+    return std::min(BW_MAX_STAGES, std::min(128 * 1024, ring_bytes) / stage_bytes);
+  };
+  auto smem_for = [&](int resident, int nst) {
+    return static_cast<size_t>(1024) + static_cast<size_t>(resident) * tile_bytes +
+           static_cast<size_t>(nst) * stage_bytes;
+  };
   dim3 grid((M + p.G - 1) / p.G, static_cast<unsigned>(B * H));
+  if (D == 256) {
+    const int nst_dv = stages(1), nst_dk = stages(2);
+    if (nst_dk < 2) return FTK_ERR_UNSUPPORTED;
+    if (cudaFuncSetAttribute(sparse_bwd_dkv_kernel<256, 1>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem_for(1, nst_dv))) != cudaSuccess ||
+        cudaFuncSetAttribute(sparse_bwd_dkv_kernel<256, 2>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem_for(2, nst_dk))) != cudaSuccess)
+      return FTK_ERR_CUDA;
+    p.nstages = nst_dv;
+    sparse_bwd_dkv_kernel<256, 1><<<grid, BW_THREADS, smem_for(1, nst_dv), st>>>(tq, tdo, tk, tv, p);
+    p.nstages = nst_dk;
+    sparse_bwd_dkv_kernel<256, 2><<<grid, BW_THREADS, smem_for(2, nst_dk), st>>>(tq, tdo, tk, tv, p);
+    return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+  }
+  p.nstages = stages(2);
+  if (p.nstages < 2) return FTK_ERR_UNSUPPORTED;
+  const size_t smem = smem_for(2, p.nstages);
   if (D == 64) {
-    if (cudaFuncSetAttribute(sparse_bwd_dkv_kernel<64, 64>,
+    if (cudaFuncSetAttribute(sparse_bwd_dkv_kernel<64, 0>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return FTK_ERR_CUDA;
-    sparse_bwd_dkv_kernel<64, 64><<<grid, BW_THREADS, smem, st>>>(tq, tdo, tk, tv, p);
-  } else if (D == 256) {
-    if (cudaFuncSetAttribute(sparse_bwd_dkv_kernel<256, 128>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem)) != cudaSuccess)
-      return FTK_ERR_CUDA;
-    for (p.o_off = 0; p.o_off < 256; p.o_off += 128)
-      sparse_bwd_dkv_kernel<256, 128><<<grid, BW_THREADS, smem, st>>>(tq, tdo, tk, tv, p);
+    sparse_bwd_dkv_kernel<64, 0><<<grid, BW_THREADS, smem, st>>>(tq, tdo, tk, tv, p);
   } else {
-    if (cudaFuncSetAttribute(sparse_bwd_dkv_kernel<128, 128>,
+    if (cudaFuncSetAttribute(sparse_bwd_dkv_kernel<128, 0>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return FTK_ERR_CUDA;
-    sparse_bwd_dkv_kernel<128, 128><<<grid, BW_THREADS, smem, st>>>(tq, tdo, tk, tv, p);
+    sparse_bwd_dkv_kernel<128, 0><<<grid, BW_THREADS, smem, st>>>(tq, tdo, tk, tv, p);
   }
   return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
 }
