@@ -59,16 +59,19 @@ struct FwdParams {
   int v_off;            // first head-dim column of V / O this launch produces (head dim 256)
 };
 
-// D = head dim of the Q.K^T contraction, DV = columns of V / O per launch.
-// Head dim 256 runs as two launches with DV = 128 (p.v_off = 0, 128): two
-// 256-column accumulators do not fit TMEM next to S, and Q stays in shared
-// memory.  Both launches write the same lse.
+// D = head dim of the Q.K^T contraction, DV = columns of V / O per launch
+// (p.v_off = first column).  Head dim 256: two 256-column accumulators do not
+// fit TMEM next to S, so there is ONE accumulator (columns 256..511) and one
+// softmax group with one running maximum drains both S buffers in turn; Q
+// stays in shared memory.  The tile's UMMAs (16 + 4 k-steps) outlast its
+// softmax, so one group keeps up.  The second group only helps in the epilogue.
 template <int D, int DV>
 __global__ void __launch_bounds__(FW_THREADS, 1)
 sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
   constexpr int NCH = D / 64;
   constexpr int NCV = DV / 64;
+  constexpr bool SINGLE = DV > 128;     // one O accumulator, one softmax group
   constexpr int Q_BYTES = NCH * 128 * 128;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -200,8 +203,9 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int ksteps = p.kvb / 16;
         if (elect_one()) {
           for (int ks = 0; ks < ksteps; ks++) {
-            umma_ts(tmem + FW_COL_O + sb * 128, tmem + s_col0 + sb * s_stride + ks * 8,
-                    desc_advance(vdesc, ks * 2048), idesc_pv, (i >= 2) || (ks > 0));
+            umma_ts(tmem + FW_COL_O + (SINGLE ? 0 : sb * 128),
+                    tmem + s_col0 + sb * s_stride + ks * 8, desc_advance(vdesc, ks * 2048),
+                    idesc_pv, (i >= (SINGLE ? 1 : 2)) || (ks > 0));
           }
           umma_commit(bar_kvempty(s));
         }
@@ -222,8 +226,7 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int qrow = tile_row0 + r;
     const bool row_valid = (grp < groups) && qrow >= 0 && qrow < p.N;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t s_addr = lane_addr + s_col0 + grp_w * s_stride;
-    const uint32_t o_addr = lane_addr + FW_COL_O + grp_w * 128;
+    const uint32_t o_addr = lane_addr + FW_COL_O + (SINGLE ? 0 : grp_w * 128);
     const float c = p.scale_log2;
     float m_run = -INFINITY, l = 0.f;
     bool ok = true;
@@ -254,14 +257,28 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (lane == 0) mbar_arrive(bar_qt);
     }
 
-    for (int i = grp_w; ok && i < n; i += 2) {
+    for (int i = SINGLE ? (grp_w == 0 ? 0 : n) : grp_w; ok && i < n; i += SINGLE ? 1 : 2) {
       // S(i) complete also means PV(i-2) has retired (same issue order), so
-      // this group's O accumulator and P columns are free to touch.
-      if (!mbar_wait(bar_sfull(grp_w), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) {
+      // this buffer's P columns (and with two groups: this group's O
+      // accumulator) are free to touch.
+      const int sbuf = SINGLE ? (i & 1) : grp_w;
+      const uint32_t s_addr = lane_addr + s_col0 + sbuf * s_stride;
+      if (!mbar_wait(bar_sfull(sbuf), (i >> 1) & 1, w, FTK_DEV_TIMEOUT_CONSUMER)) {
         ok = false;
         break;
       }
       tc_fence_after();
+      // One shared accumulator: PV(i-1) may still be adding to it.  A thread
+      // that has to rescale it first waits until that UMMA has retired (the
+      // commit that hands tile i-1's K / V stage back to the producer).
+      auto o_quiet = [&]() -> bool {
+        if (!SINGLE || i == 0) return true;
+        const int sp = (i - 1) % NST;
+        if (!mbar_wait(bar_kvempty(sp), ((i - 1) / NST) & 1, w, FTK_DEV_TIMEOUT_CONSUMER))
+          return false;
+        tc_fence_after();
+        return true;
+      };
       const int tok0 = static_cast<int>(un.ids[i]) * p.kvb - p.kv_pad_head;
       const int lo = max(0, -tok0), hi = min(p.kvb, p.N - tok0);
       const bool act = row_valid && ((un.masks[i] >> grp) & 1) && hi > lo;
@@ -291,6 +308,10 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const float m_new = grow ? mt2 : m_run;
         const bool resc = grow && l > 0.f;
         if (__any_sync(0xffffffffu, resc)) {
+          if (!o_quiet()) {
+            ok = false;
+            break;
+          }
           const float alpha = resc ? fast_exp2(m_run - m_new) : 1.f;
           for (int c0 = 0; c0 < DV; c0 += 32) {
             uint32_t ov[32];
@@ -353,6 +374,10 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const float m_new = grow ? mt2 : m_run;
         const bool resc = grow && l > 0.f;
         if (__any_sync(0xffffffffu, resc)) {
+          if (!o_quiet()) {
+            ok = false;
+            break;
+          }
           const float alpha = resc ? fast_exp2(m_run - m_new) : 1.f;
           for (int c0 = 0; c0 < DV; c0 += 32) {
             uint32_t ov[32];
@@ -391,7 +416,7 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pfull(grp_w));
+      if (lane == 0) mbar_arrive(bar_pfull(sbuf));
     }
 
     // ------------------------------------------------------------ epilogue
@@ -421,7 +446,7 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       for (int c0 = grp_w * HALF; c0 < (grp_w + 1) * HALF; c0 += 32) {
         uint32_t va[32], vb[32];
         if (n > 0) tmem_ld32(lane_addr + FW_COL_O + c0, va);
-        if (n > 1) tmem_ld32(lane_addr + FW_COL_O + 128 + c0, vb);
+        if (!SINGLE && n > 1) tmem_ld32(lane_addr + FW_COL_O + 128 + c0, vb);
         if (n > 0) tmem_wait_ld();
         if (row_valid) {
           uint32_t pk[16];
@@ -431,7 +456,7 @@ sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (have) {
               a = __uint_as_float(va[x]) * wa;
               b = __uint_as_float(va[x + 1]) * wa;
-              if (n > 1) {
+              if (!SINGLE && n > 1) {
                 a = fmaf(__uint_as_float(vb[x]), wb, a);
                 b = fmaf(__uint_as_float(vb[x + 1]), wb, b);
               }
@@ -614,6 +639,6 @@ extern "C" int ftk_sparse_fwd(const void* q, const void* k, const void* v, int d
     p.redo_in = static_cast<const int*>(workspace);
   }
   if (D == 64) return launch_fwd<64>(tq, tk, tv, p, B * H, st);
-  if (D == 256) return launch_fwd<256, 128>(tq, tk, tv, p, B * H, st);
+  if (D == 256) return launch_fwd<256, 256>(tq, tk, tv, p, B * H, st);
   return launch_fwd<128>(tq, tk, tv, p, B * H, st);
 }

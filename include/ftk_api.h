@@ -202,8 +202,8 @@ int ftk_sort_by_count(const int32_t* counts, int64_t total, int max_count,
  * exact kernel runs.  Setting the environment variable FTK_FWD_PIPE=0 does the
  * same.  At head dim 128 the pipelined kernel runs on pairs of SMs (clusters of
  * two CTAs, tcgen05 cta_group::2); FTK_FWD_2CTA=0 selects the one-CTA form.
- * Head dim 256 (D is 64, 128 or 256) runs the exact kernel as two launches of
- * 128 output columns (dK / dV: one launch for dV, one for dK);
+ * Head dim 256 (D is 64, 128 or 256) runs the exact kernel with one shared
+ * output accumulator (dK / dV: one launch for dV, one for dK);
  * ftk_sparse_bwd_dq and ftk_sparse_bwd_dkv then take kv
  * blocks (dq) and q blocks (dkv) of at most 32 rows and return
  * FTK_ERR_UNSUPPORTED otherwise: the host layer restates longer blocks over

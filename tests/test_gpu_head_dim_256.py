@@ -85,6 +85,34 @@ def test_attention_forward(ftk, D, dtype, g, kvb, N, qpad, kvpad):
     _close(lse.cpu().numpy(), wl, "lse")
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+def test_forward_rescales_shared_accumulator(ftk, dtype):
+    """Later kv blocks carry much larger logits, so the running maximum grows
+    several times and the one O accumulator is rescaled while the previous
+    tile's P.V may still be in flight."""
+    H, N, D, g, kvb = 2, 512, 256, 64, 64
+    cfg = dict(B=1, N=N, H=H, D=D, dtype=dtype, seed=47, do_seed=48)
+    t = cases.make_inputs(cfg)
+    boost = torch.tensor([1, 1, 5, 1, 9, 2, 14, 20], dtype=torch.float32)
+    k = (t["k"].float().view(1, N // kvb, kvb, H * D) * boost.view(1, -1, 1, 1)).view(1, N, H * D)
+    t["k"] = k.to(t["q"].dtype)
+    x = {n: v.float().numpy() for n, v in t.items()}
+    QM, M = N // g, N // kvb
+    merged = np.tile(np.arange(M, dtype=np.int32), (1, H, QM, 1))
+    merged[0, 1, 3, 5:] = -1
+    q, kk, v = (t[n].cuda() for n in "qkv")
+    o, lse = ftk.flash_topk_attn(q, kk, v, torch.from_numpy(merged).cuda(), None, H, g, kvb)
+    ftk.check_errors()
+    wo, wl = orc.sparse_attn_fwd(x["q"], x["k"], x["v"], merged, H, g, kvb)
+    # nearly one-hot rows: O is one bf16-rounded P times values of size 2..4, so the
+    # bf16 bound is that of the output's own rounding (as for the other one-hot cases)
+    got, want = o.float().cpu().numpy().astype(np.float64), np.asarray(wo, np.float64)
+    atol = 2e-2 if dtype == "bf16" else ATOL
+    assert (np.abs(got - want) <= atol + RTOL * np.abs(want)).all(), \
+        float(np.abs(got - want).max())
+    _close(lse.cpu().numpy(), wl, "lse")
+
+
 @pytest.mark.parametrize("D,dtype,g,kvb,N,qpad,kvpad", [
     (256, "bf16", 64, 64, 512, (0, 0), (0, 0)),       # lists restated over 32-row blocks
     (256, "fp16", 32, 64, 300, (10, 10), (40, 44)),
