@@ -494,10 +494,13 @@ class FlashSparseAttnFunc(torch.autograd.Function):
             # head dim 256: the gradient kernels hold Q / dO (dQ) or K / V (dK, dV) of 256
             # columns in shared memory and have room for 32-row partner tiles only
             for name, blk in (("q_block_size", g), ("kv_block_size", kvb)):
-                if blk > 32 and blk % 32 != 0:
+                part = blk
+                while part > 32 and part % 2 == 0:
+                    part //= 2
+                if part > 32 or part % 16 != 0:
                     raise NotImplementedError(
-                        f"backward at head dim > 128 needs {name} <= 32 or a multiple of 32, "
-                        f"got {blk}")
+                        f"backward at head dim > 128 needs a {name} that halves down to 16 or "
+                        f"32 rows (16, 32, 64, 128), got {blk}")
             merged, g, kvb, qph, kph, M = _split_large_blocks(merged, N, g, kvb, qph, kph, 32)
         do, sdo_b, sdo_n, sdo_h = _as_bnhd(grad_o.to(qq.dtype), False, H, D)
         _, sq_b, sq_n, sq_h = _as_bnhd(qq, False, H, D)
