@@ -32,11 +32,14 @@ import torch
 from flash_topk_attn_v2 import ops
 from flash_topk_attn_v2.ops import flash_sparse_attn
 
+Pair = Tuple[int, int]
+Tensor = torch.Tensor
+
 _NO_CUT = 2.0   # cumulative block mass never reaches 2: the threshold never fires
 _DENSE_BLOCK = 64
 
 
-def _to_bnc(x: torch.Tensor) -> torch.Tensor:
+def _to_bnc(x: Tensor) -> Tensor:
     B, H, N, D = x.shape
     return x.transpose(1, 2).reshape(B, N, H * D)
 
@@ -56,17 +59,9 @@ def _dense_attention(q, k, v, num_heads):
     return o
 
 
-def flash_topk_score(
-    q: torch.Tensor,
-    k: torch.Tensor,
-    v: Optional[torch.Tensor] = None,
-    num_heads: Optional[int] = None,
-    score_block_size: int = 64,
-    topk: int = 16,
-    padding: Tuple[int, int] = (0, 0),
-    score_only: bool = False,
-    backend: str = "triton",
-):
+def flash_topk_score(q: Tensor, k: Tensor, v: Optional[Tensor] = None,
+                     num_heads: Optional[int] = None, score_block_size: int = 64, topk: int = 16,
+                     padding: Pair = (0, 0), score_only: bool = False, backend: str = "triton"):
     """(o, topk_indices, topk_scores), or (topk_indices, topk_scores) with
     `score_only=True` (reference flash_topk_attn/scoring.py:1289-1357).
     `backend` keeps the reference's only accepted value."""
@@ -109,11 +104,8 @@ def flash_topk_score(
     return o, idx, scores
 
 
-def build_qblock_topk_indices(
-    topk_indices: torch.Tensor,
-    q_block_size: int,
-    q_padding: Tuple[int, int] = (0, 0),
-) -> Tuple[torch.Tensor, torch.Tensor, int]:
+def build_qblock_topk_indices(topk_indices: Tensor, q_block_size: int,
+                              q_padding: Pair = (0, 0)) -> Tuple[Tensor, Tensor, int]:
     """Sorted distinct block ids per q-block: (merged [B, H, QM, S_MAX] int32,
     counts [B, H, QM] int32, S_MAX = next_pow2(q_block_size * K))
     (reference flash_topk_attn/attention.py:70-138)."""
@@ -137,21 +129,11 @@ def build_qblock_topk_indices(
     return merged, counts, merged.shape[-1]
 
 
-def flash_topk_attn(
-    q: torch.Tensor,
-    k: torch.Tensor,
-    v: torch.Tensor,
-    merged_indices: torch.Tensor,
-    counts: torch.Tensor,
-    num_heads: int,
-    q_block_size: int,
-    kv_block_size: int,
-    scale: Optional[float] = None,
-    num_kv_heads: Optional[int] = None,
-    kv_padding: Tuple[int, int] = (0, 0),
-    q_padding: Tuple[int, int] = (0, 0),
-    S_MAX: Optional[int] = None,
-) -> Tuple[torch.Tensor, torch.Tensor]:
+def flash_topk_attn(q: Tensor, k: Tensor, v: Tensor, merged_indices: Tensor, counts: Tensor,
+                    num_heads: int, q_block_size: int, kv_block_size: int,
+                    scale: Optional[float] = None, num_kv_heads: Optional[int] = None,
+                    kv_padding: Pair = (0, 0), q_padding: Pair = (0, 0),
+                    S_MAX: Optional[int] = None) -> Tuple[Tensor, Tensor]:
     """(o [B, N, C], lse [B, H, N] fp32): every query of a q-block attends
     over the tokens of the first counts[b, h, m] listed blocks (reference
     flash_topk_attn/attention.py:423-568).  Unlike the reference this call is
