@@ -29,13 +29,38 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "flash-topk-attention_b200"))
 sys.path.insert(0, ROOT)
 
+# The CPU legs use every host core whatever launched this process: torchrun
+# exports OMP_NUM_THREADS=1, which the BLAS behind numpy reads when it loads.
+HOST_CORES = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()
+if "reference" in sys.argv:
+    for _v in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[_v] = str(HOST_CORES)
+
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
 WORKLOAD = dict(
     name="config2-e2e", B=1, N=32768, H=32, D=128, dtype="bf16", input_scale=0.5,
     score_block_size=64, topk=32, threshold=0.9, q_block_size=64, kv_block_size=64,
+    qblock_topk=None,
 )
+# Side workloads (--workload): the other BASELINE.json shapes, per GPU.  The
+# headline line always comes from WORKLOAD above.
+WORKLOADS = {
+    "config2-e2e": WORKLOAD,
+    # configs[0]: the reference's CPU-runnable shape
+    "config1": dict(name="config1", B=2, N=1024, H=8, D=64, dtype="fp16", input_scale=1.0,
+                    score_block_size=64, topk=16, threshold=1.0, q_block_size=32,
+                    kv_block_size=64, qblock_topk=None),
+    # configs[2]: full training step, score-weighted merge to 256 blocks
+    "config3": dict(name="config3", B=4, N=8192, H=16, D=128, dtype="bf16", input_scale=1.0,
+                    score_block_size=64, topk=16, threshold=1.0, q_block_size=64,
+                    kv_block_size=64, qblock_topk=256),
+    # configs[4]: one batch element (64 of its 512 slices) per GPU
+    "config5": dict(name="config5", B=1, N=65536, H=64, D=128, dtype="bf16", input_scale=1.0,
+                    score_block_size=64, topk=64, threshold=1.0, q_block_size=64,
+                    kv_block_size=64, qblock_topk=None),
+}
 METRIC = "score+sparse fwd+bwd tokens/s @N=32k,H=32,D=128 bf16"
 UNIT = "tokens/s"
 
@@ -80,11 +105,12 @@ def make_host_inputs(cfg, seed):
     g = torch.Generator().manual_seed(seed)
     shape = (cfg["B"], cfg["N"], cfg["H"] * cfg["D"])
     s = cfg["input_scale"]
+    dt = torch.float16 if cfg.get("dtype") == "fp16" else torch.bfloat16
     out = {}
     for name in ("q", "k", "v"):
-        out[name] = (torch.randn(shape, generator=g) * s).to(torch.bfloat16).pin_memory()
+        out[name] = (torch.randn(shape, generator=g) * s).to(dt).pin_memory()
     g2 = torch.Generator().manual_seed(1000 + seed)
-    out["do"] = torch.randn(shape, generator=g2).to(torch.bfloat16).pin_memory()
+    out["do"] = torch.randn(shape, generator=g2).to(dt).pin_memory()
     return out
 
 
@@ -161,7 +187,7 @@ def run_ours(args):
         dist = dist_mod
         dist.init_process_group("nccl", device_id=dev)
 
-    cfg = dict(WORKLOAD)
+    cfg = dict(WORKLOADS[args.workload])
     if args.small:
         cfg.update(N=8192, H=16, name="small")
     if args.head_dim != cfg["D"]:
@@ -188,7 +214,8 @@ def run_ours(args):
         idx, raw, avg = ftk.flash_topk_score(q.detach(), k.detach(), H, b, K, (0, 0), thr)
         if record:
             evs[1].record()
-        merged, counts, W = ftk.build_qblock_topk_indices(idx, g, topk_scores=avg)
+        merged, counts, W = ftk.build_qblock_topk_indices(idx, g, topk_scores=avg,
+                                                          qblock_topk=cfg["qblock_topk"])
         if record:
             evs[2].record()
         if before_attn is not None:

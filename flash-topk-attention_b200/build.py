@@ -67,5 +67,26 @@ def build(force: bool = False) -> str:
     return LIB
 
 
+PROBE_SRC = os.path.join(os.path.dirname(HERE), "tests", "native", "wait_probe.cu")
+PROBE_LIB = os.path.join(os.path.dirname(HERE), "tests", "native", "libftk_wait_probe.so")
+
+
+def build_wait_probe(force: bool = False) -> str:
+    """Test-only library: the bounded waits of csrc/ftk_sm100.cuh compiled with a
+    wait limit of 200 000 clock ticks (tests/native/wait_probe.cu)."""
+    if not os.path.exists(PROBE_SRC):
+        return ""
+    newest = max(os.path.getmtime(PROBE_SRC), _headers_mtime())
+    if not force and os.path.exists(PROBE_LIB) and os.path.getmtime(PROBE_LIB) >= newest:
+        return PROBE_LIB
+    cmd = [NVCC, *FLAGS, "-DFTK_WAIT_CYCLES=200000LL", "-I", CSRC, "-shared", "-cudart", "static",
+           PROBE_SRC, "-o", PROBE_LIB]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for wait_probe.cu:\n{r.stdout}\n{r.stderr}")
+    return PROBE_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv))
+    print(build_wait_probe(force="--force" in sys.argv))

@@ -62,6 +62,8 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
 
 // Per-CTA abort plumbing: `abort_flag` lives in shared memory, `status` in
 // global memory (one word per launch, zeroed by the host before the launch).
+// `status` may be null (the caller passed no status word): the abort flag alone
+// still unwinds the CTA, only the code is lost.
 struct WaitCtx {
   volatile int* abort_flag;
   int* status;
@@ -78,7 +80,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
       if (*w.abort_flag) return false;
       if (clock64() - t0 > FTK_WAIT_CYCLES) {
         *w.abort_flag = 1;
-        atomicCAS(w.status, 0, code);
+        if (w.status) atomicCAS(w.status, 0, code);
         return false;
       }
     }
@@ -108,7 +110,7 @@ __device__ __forceinline__ bool mbar_wait_all(const uint32_t (&bar)[N], const ui
       if (*w.abort_flag) return false;
       if (clock64() - t0 > FTK_WAIT_CYCLES) {
         *w.abort_flag = 1;
-        atomicCAS(w.status, 0, code);
+        if (w.status) atomicCAS(w.status, 0, code);
         return false;
       }
     }

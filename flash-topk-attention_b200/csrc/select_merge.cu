@@ -475,6 +475,191 @@ qblock_merge_kernel(const int32_t* __restrict__ idx, const float* __restrict__ s
   if (tid == 0 && counts) counts[qb] = cnt_s;
 }
 
+// Bitonic network over 32*E values held E per lane in BLOCKED order (position
+// p = lane*E + r), sorted largest first.  Strides below E stay inside a lane
+// (registers only); only the log2(32) largest strides of each merge cross
+// lanes, so a 512-key sort needs 15 shuffle stages where the striped layout of
+// bitonic_desc needs 35.
+template <int E, typename T>
+__device__ __forceinline__ void bitonic_desc_blocked(T (&v)[E], int lane) {
+  constexpr int N = 32 * E;
+#pragma unroll
+  for (int k = 2; k <= N; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      if (j < E) {
+#pragma unroll
+        for (int r = 0; r < E; r++) {
+          if ((r & j) == 0) {
+            // k < E: the direction bit is a bit of r, else a bit of the lane
+            const bool desc = (k < E) ? ((r & k) == 0) : ((lane & (k / E)) == 0);
+            const T x = v[r], y = v[r | j];
+            const bool sw = desc ? (x < y) : (x > y);
+            v[r] = sw ? y : x;
+            v[r | j] = sw ? x : y;
+          }
+        }
+      } else {
+        const int jl = j / E;
+        const bool lower = (lane & jl) == 0;
+        const bool desc = (lane & (k / E)) == 0;
+        const bool take_max = (desc == lower);
+#pragma unroll
+        for (int r = 0; r < E; r++) {
+          const T o = __shfl_xor_sync(0xffffffffu, v[r], jl);
+          const bool o_gt = o > v[r];
+          v[r] = (take_max == o_gt) ? o : v[r];
+        }
+      }
+    }
+  }
+}
+
+// Merge with ONE WARP per q-block, for tables of up to 32*E <= 1024 block ids
+// (every BASELINE shape).  Same arithmetic as qblock_merge_kernel: the entries
+// of the q-block are walked in (row, rank) order, 32 at a time, entries of one
+// step that name the same block are applied in lane order, so every aggregate
+// is the same fp32 sum in the same order.  No block-wide barrier: the warp
+// zeroes its own table in shared memory, adds into it (one match per step finds
+// repeats), builds 64-bit keys (aggregate bits : ~block id) in registers,
+// sorts them with the blocked bitonic network and writes its row, the -1 / 0
+// tail with 16-byte stores.
+constexpr int MGW_WARPS = 4;
+
+template <int E>
+__global__ void __launch_bounds__(MGW_WARPS * 32)
+qblock_merge_warp_kernel(const int32_t* __restrict__ idx, const float* __restrict__ scr, int64_t N,
+                         int K, int g, int q_pad_head, int QM, int64_t total_qb, int Mtot, int W,
+                         int32_t* __restrict__ out_idx, float* __restrict__ out_scr,
+                         int32_t* __restrict__ counts, int* status) {
+  constexpr int MP = 32 * E;
+  __shared__ float agg_all[MGW_WARPS][MP];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t qb = static_cast<int64_t>(blockIdx.x) * MGW_WARPS + warp;  // bh * QM + m
+  if (qb >= total_qb) return;
+  float* agg = agg_all[warp];
+  const int64_t bh = qb / QM;
+  const int m = static_cast<int>(qb - bh * QM);
+#pragma unroll
+  for (int r = 0; r < E; r++) agg[r * 32 + lane] = 0.f;
+  __syncwarp();
+
+  const int t0 = m * g - q_pad_head;
+  const int r0 = max(t0, 0);
+  const int r1 = static_cast<int>(min(static_cast<long long>(N), static_cast<long long>(t0) + g));
+  if (r1 > r0) {
+    const int64_t base = (bh * N + r0) * K;
+    const int total = (r1 - r0) * K;
+    constexpr int U = 4;   // steps fetched together
+    for (int e0 = 0; e0 < total; e0 += 32 * U) {
+      int jj[U];
+      float ss[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const int e = e0 + u * 32 + lane;
+        jj[u] = -1;
+        ss[u] = 0.f;
+        if (e < total) {
+          jj[u] = __ldg(idx + base + e);
+          ss[u] = scr ? __ldg(scr + base + e) : 1.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        if (e0 + u * 32 >= total) break;   // warp-uniform
+        int j = jj[u];
+        if (j >= Mtot) {
+          if (status) atomicCAS(status, 0, FTK_DEV_BAD_INDEX);
+          j = -1;
+        }
+        const bool act = j >= 0;
+        const unsigned grp = __match_any_sync(0xffffffffu, act ? j : -1 - lane);
+        const int mult = act ? __popc(grp) : 1;
+        if (__all_sync(0xffffffffu, mult == 1)) {
+          if (act) agg[j] += ss[u];
+        } else {
+          const int rank = __popc(grp & ((1u << lane) - 1u));
+          const int rounds = redux_max_s32(mult);
+          for (int rd = 0; rd < rounds; rd++) {
+            if (act && rank == rd) agg[j] += ss[u];
+            __syncwarp();
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }
+  __syncwarp();
+
+  // any assignment of ids to sort positions will do: read the table bank by bank
+  unsigned long long key[E];
+  int nz = 0;
+#pragma unroll
+  for (int r = 0; r < E; r++) {
+    const int j = r * 32 + lane;
+    const float a = agg[j];
+    key[r] = 0ull;
+    if (j < Mtot && a > 0.f) {
+      key[r] = (static_cast<unsigned long long>(__float_as_uint(a)) << 32) |
+               static_cast<unsigned long long>(0xffffffffu - static_cast<unsigned>(j));
+      nz++;
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) nz += __shfl_xor_sync(0xffffffffu, nz, d);
+  bitonic_desc_blocked<E>(key, lane);
+
+  int32_t* oi = out_idx + qb * W;
+  float* os = out_scr ? out_scr + qb * W : nullptr;
+  int ids[E];
+  float scs[E];
+#pragma unroll
+  for (int r = 0; r < E; r++) {
+    ids[r] = key[r] ? static_cast<int>(0xffffffffu - static_cast<unsigned>(key[r] & 0xffffffffull))
+                    : -1;
+    scs[r] = __uint_as_float(static_cast<unsigned>(key[r] >> 32));
+  }
+  const bool vec = (W & 3) == 0 && (reinterpret_cast<uintptr_t>(out_idx) & 15) == 0 &&
+                   (!out_scr || (reinterpret_cast<uintptr_t>(out_scr) & 15) == 0);
+  const int p0 = lane * E;   // first rank held by this lane
+  if (E >= 4 && vec) {
+#pragma unroll
+    for (int r = 0; r < E; r += 4) {
+      if (p0 + r < W) {      // W % 4 == 0: the whole quad is inside the row
+        *reinterpret_cast<int4*>(oi + p0 + r) = make_int4(ids[r], ids[r + 1], ids[r + 2], ids[r + 3]);
+        if (os)
+          *reinterpret_cast<float4*>(os + p0 + r) =
+              make_float4(scs[r], scs[r + 1], scs[r + 2], scs[r + 3]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < E; r++) {
+      if (p0 + r < W) {
+        oi[p0 + r] = ids[r];
+        if (os) os[p0 + r] = scs[r];
+      }
+    }
+  }
+  if (W > MP) {
+    if (vec) {
+      int4* o4 = reinterpret_cast<int4*>(oi);
+      float4* s4 = reinterpret_cast<float4*>(os);
+      for (int x = (MP >> 2) + lane; x < (W >> 2); x += 32) {
+        o4[x] = make_int4(-1, -1, -1, -1);
+        if (os) s4[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    } else {
+      for (int x = MP + lane; x < W; x += 32) {
+        oi[x] = -1;
+        if (os) os[x] = 0.f;
+      }
+    }
+  }
+  // valid entries form a prefix of the row
+  if (lane == 0 && counts) counts[qb] = min(nz, W);
+}
+
 // Exact union of a q-block's per-row picks, ascending by block id.  Replaces
 // _build_qblock_indices_kernel of the first-generation operators
 // (flash_topk_attn/attention.py:23-67: load, sort, drop repeats, compact).
@@ -807,6 +992,25 @@ extern "C" int ftk_qblock_merge(const int32_t* topk_idx, const float* topk_score
   const int Mp = std::max(32, next_pow2(num_score_blocks));
   const size_t smem = static_cast<size_t>(Mp) * 12;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (Mp <= 1024) {
+    // one warp per q-block
+    const int64_t total_qb = BH * QM;
+    const unsigned grid = static_cast<unsigned>((total_qb + MGW_WARPS - 1) / MGW_WARPS);
+#define FTK_MGW(E)                                                                          \
+  qblock_merge_warp_kernel<E><<<grid, MGW_WARPS * 32, 0, st>>>(                             \
+      topk_idx, topk_scores, N, K, q_block_size, q_pad_head, static_cast<int>(QM), total_qb, \
+      num_score_blocks, qblock_topk, merged_idx, merged_scores, counts, status)
+    switch (Mp) {
+      case 32: FTK_MGW(1); break;
+      case 64: FTK_MGW(2); break;
+      case 128: FTK_MGW(4); break;
+      case 256: FTK_MGW(8); break;
+      case 512: FTK_MGW(16); break;
+      default: FTK_MGW(32); break;
+    }
+#undef FTK_MGW
+    return cudaGetLastError() == cudaSuccess ? FTK_OK : FTK_ERR_CUDA;
+  }
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(qblock_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(smem)) != cudaSuccess)

@@ -67,20 +67,31 @@ def flash_topk_score(q: Tensor, k: Tensor, num_heads: Optional[int] = None,
 
 def build_qblock_topk_indices(topk_indices: Tensor, q_block_size: int, q_padding: Pair = (0, 0),
                               topk_scores: Optional[Tensor] = None,
-                              qblock_topk: Optional[int] = None) -> Tuple[Tensor, Tensor, int]:
+                              qblock_topk: Optional[int] = None,
+                              num_score_blocks: Optional[int] = None) -> Tuple[Tensor, Tensor, int]:
     """Per-q-block merged indices: (merged [B,H,QM,W] int32, counts [B,H,QM]
-    int32, W) (reference __init__.py:57-133)."""
+    int32, W) (reference __init__.py:57-133).
+
+    `num_score_blocks` (not in the reference) is an upper bound of the block
+    ids, i.e. M of the scoring call; any bound >= max(valid id) + 1 gives the
+    same result.  Without it the bound is taken from the index tensor when
+    flash_topk_score of this package made it (the tensor carries M), and
+    otherwise read back from the device as the reference does (one host
+    synchronisation; under stream capture, where that is not allowed, the
+    largest supported table, 4096 blocks, is used instead)."""
     if topk_indices.ndim != 4:
         raise ValueError("topk_indices must be [B, H, N, K]")
     rows, picks = topk_indices.shape[2:]
     _check_q_blocks(rows, q_block_size, q_padding)
     width = q_block_size * picks if qblock_topk is None else qblock_topk
-    # size of the aggregation table: any bound >= max(valid id) + 1 gives the
-    # same result.  Index tensors made by flash_topk_score carry the block
-    # count; otherwise read the maximum back as the reference does.
-    blocks = getattr(topk_indices, "_ftk_num_score_blocks", None)
+    blocks = num_score_blocks
     if blocks is None:
-        blocks = max(int(topk_indices.max().item()) + 1, 1) if topk_indices.numel() else 1
+        blocks = getattr(topk_indices, "_ftk_num_score_blocks", None)
+    if blocks is None:
+        if topk_indices.is_cuda and torch.cuda.is_current_stream_capturing():
+            blocks = 4096
+        else:
+            blocks = ops.num_score_blocks_of(topk_indices)
     merged, _, counts = flash_qblock_merge(topk_indices, topk_scores, q_block_size, width, blocks,
                                            q_padding=tuple(q_padding), return_counts=True)
     return merged, counts, merged.shape[-1]

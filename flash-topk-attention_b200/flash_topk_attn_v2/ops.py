@@ -317,6 +317,19 @@ def flash_topk_score_fused(q, k, num_heads, score_block_size, topk, padding, thr
 # --------------------------------------------------------------------------
 # merge
 # --------------------------------------------------------------------------
+def num_score_blocks_of(topk_indices) -> int:
+    """max(valid id) + 1 (at least 1) of an index tensor: one device reduction
+    (ftk_max_index_plus1) and one four-byte read-back, where the reference
+    masks, gathers and reduces with PyTorch (__init__.py:101-105)."""
+    idx = topk_indices.to(torch.int32).contiguous()
+    dev = idx.device
+    out = torch.empty(1, dtype=torch.int32, device=dev)
+    _call("ftk_max_index_plus1", lib.ftk_max_index_plus1, ptr(idx), idx.numel(), ptr(out),
+          stream_ptr(dev))
+    _count(2 if idx.numel() else 1)
+    return int(out.item())
+
+
 def flash_qblock_merge(topk_indices, topk_scores, q_block_size, qblock_topk, num_score_blocks,
                        q_padding=(0, 0), return_counts=False):
     """Per-q-block aggregation + ranking of (block, score) pairs.

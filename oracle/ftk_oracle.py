@@ -38,6 +38,8 @@ __all__ = [
     "qblock_merge",
     "build_qblock_topk_indices",
     "sparse_attn_fwd",
+    "round_to_dtype",
+    "UNIT_ROUNDOFF",
     "sparse_attn_bwd",
     "preprocess_delta",
     "build_reverse_indices",
@@ -333,9 +335,28 @@ def _kv_token_mask(blocks: np.ndarray, n: int, kvb: int, kv_pad_head: int):
     return mask
 
 
+def round_to_dtype(x: np.ndarray, dtype: str) -> np.ndarray:
+    """Round to the nearest fp16 / bf16 value (ties to even), kept in x's dtype."""
+    x = np.asarray(x)
+    if dtype == "fp16":
+        return x.astype(np.float16).astype(x.dtype)
+    if dtype != "bf16":
+        raise ValueError(dtype)
+    f = np.ascontiguousarray(x, dtype=np.float32)
+    u = f.view(np.uint32).astype(np.uint64)
+    u = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    out = u.astype(np.uint32).view(np.float32).reshape(f.shape)
+    return np.where(np.isfinite(f), out, f).astype(x.dtype)
+
+
+# unit roundoff (half an ulp, relative) of the two 16-bit formats
+UNIT_ROUNDOFF = {"fp16": 2.0 ** -12, "bf16": 2.0 ** -9}
+
+
 def sparse_attn_fwd(
     q, k, v, merged_indices, num_heads, q_block_size, kv_block_size,
     scale=None, q_padding=(0, 0), kv_padding=(0, 0), work=np.float64,
+    roundings=None, io_dtype=None, envelope=False,
 ):
     """Gathered-KV attention per q-block: returns (O [B,N,C], lse [B,H,N]).
 
@@ -343,7 +364,22 @@ def sparse_attn_fwd(
     its candidate KV blocks; an empty candidate set gives O = 0, lse = -inf.
     Restates `_flash_sparse_attn_naive`
     (flash_topk_attn_v2/sparse_attn.py:24-127); O is left unrounded.
+
+    `roundings="reference"` (with `io_dtype` "fp16" | "bf16") applies the
+    roundings of the reference's GPU kernel on top of exact arithmetic: the
+    probabilities exp(s - rowmax) are rounded to the I/O dtype before P.V
+    while the row sum uses the unrounded ones
+    (csrc/sparse_attn_kernel.cu:282-309), and O is rounded to the I/O dtype
+    when stored (:333-342).  The kernel rounds against its running maximum;
+    here the final row maximum is used, which moves individual roundings but
+    not their size.  `envelope=True` additionally returns a first-order
+    worst-case bound on |O_rounded - O_exact| per element (u * sum_i P_i |v_i|
+    / l for the rounding of P plus u |O| for the store), u the unit roundoff.
     """
+    if roundings not in (None, "reference"):
+        raise ValueError(f"roundings must be None or 'reference', got {roundings!r}")
+    if (roundings or envelope) and io_dtype not in UNIT_ROUNDOFF:
+        raise ValueError("io_dtype must be 'fp16' or 'bf16'")
     b, n, c = q.shape
     h = num_heads
     d = c // h
@@ -362,7 +398,9 @@ def sparse_attn_fwd(
     kk = _split_heads(k, h).astype(work)
     vv = _split_heads(v, h).astype(work)
     out = np.zeros((b, h, n, d), dtype=work)
+    env = np.zeros((b, h, n, d), dtype=work) if envelope else None
     lse = np.full((b, h, n), -np.inf, dtype=work)
+    u = UNIT_ROUNDOFF.get(io_dtype, 0.0)
     for bi in range(b):
         for hi in range(h):
             for m in range(qm):
@@ -381,9 +419,19 @@ def sparse_attn_fwd(
                 mx = s.max(axis=1, keepdims=True)
                 p = np.exp(s - mx)
                 l = p.sum(axis=1, keepdims=True)
-                out[bi, hi, r0:r1] = (p / l) @ vv[bi, hi, tok]
+                if roundings:
+                    out[bi, hi, r0:r1] = (round_to_dtype(p, io_dtype) @ vv[bi, hi, tok]) / l
+                else:
+                    out[bi, hi, r0:r1] = (p / l) @ vv[bi, hi, tok]
+                if envelope:
+                    env[bi, hi, r0:r1] = u * ((p / l) @ np.abs(vv[bi, hi, tok]))
                 lse[bi, hi, r0:r1] = (mx + np.log(l))[:, 0]
     o = out.transpose(0, 2, 1, 3).reshape(b, n, c)
+    if roundings:
+        o = round_to_dtype(o, io_dtype)
+    if envelope:
+        e = env.transpose(0, 2, 1, 3).reshape(b, n, c) + u * np.abs(o)
+        return o, lse, e
     return o, lse
 
 
@@ -400,7 +448,7 @@ def preprocess_delta(o: np.ndarray, do: np.ndarray, num_heads: int) -> np.ndarra
 def sparse_attn_bwd(
     q, k, v, o, lse, do, merged_indices, num_heads, q_block_size,
     kv_block_size, scale=None, q_padding=(0, 0), kv_padding=(0, 0),
-    work=np.float64,
+    work=np.float64, roundings=None, io_dtype=None, envelope=False, o_envelope=None,
 ):
     """Closed-form gradients of sparse_attn_fwd: (dQ, dK, dV), each [B,N,C].
 
@@ -410,7 +458,21 @@ def sparse_attn_bwd(
     (flash_topk_attn_v2/sparse_attn_bwd.py:111-199, 202-294).  `o` is the
     forward output as stored (rounded to the I/O dtype), as the reference
     computes delta from it (sparse_attn.py:163-175).
+
+    `roundings="reference"` (with `io_dtype`) applies the roundings of the
+    reference's GPU kernels on top of exact arithmetic: dS is rounded to the
+    I/O dtype before dS.K (csrc/sparse_attn_bwd_dq_kernel.cu:355-358), P and dS
+    before P^T.dO and dS^T.Q (csrc/sparse_attn_bwd_dkv_kernel.cu:314-317,
+    353-356), lse is the stored fp32 value and the gradients are rounded to the
+    I/O dtype when stored.  `envelope=True` additionally returns, per gradient,
+    a first-order worst-case bound on what those roundings can move an element
+    by (`o_envelope`, the forward's bound, carries the rounding of O into
+    delta); the result is (dQ, dK, dV, (eQ, eK, eV)).
     """
+    if roundings not in (None, "reference"):
+        raise ValueError(f"roundings must be None or 'reference', got {roundings!r}")
+    if (roundings or envelope) and io_dtype not in UNIT_ROUNDOFF:
+        raise ValueError("io_dtype must be 'fp16' or 'bf16'")
     b, n, c = q.shape
     h = num_heads
     d = c // h
@@ -427,6 +489,14 @@ def sparse_attn_bwd(
     dq = np.zeros((b, h, n, d), dtype=work)
     dk = np.zeros((b, h, n, d), dtype=work)
     dv = np.zeros((b, h, n, d), dtype=work)
+    u = UNIT_ROUNDOFF.get(io_dtype, 0.0)
+    if envelope:
+        eq, ek, ev = (np.zeros((b, h, n, d), dtype=work) for _ in range(3))
+        # |error of delta| <= sum_d |error of O| |dO|
+        oe = o_envelope if o_envelope is not None else u * np.abs(o)
+        ddelta = (_split_heads(oe.astype(work), h) * np.abs(dd)).sum(axis=-1)
+    if roundings:
+        lse = np.asarray(lse, dtype=np.float32)
     for bi in range(b):
         for hi in range(h):
             for m in range(qm):
@@ -447,6 +517,16 @@ def sparse_attn_bwd(
                 p = np.exp(s - lse[bi, hi, r0:r1, None].astype(work))
                 dp = dd[bi, hi, r0:r1] @ vt.T
                 ds = p * (dp - delta[bi, hi, r0:r1, None])
+                if envelope:
+                    # rounding of dS (dQ, dK) and of P (dV), plus delta's error through P
+                    ads = u * np.abs(ds) + p * ddelta[bi, hi, r0:r1, None]
+                    qa = np.abs(qq[bi, hi, r0:r1])
+                    eq[bi, hi, r0:r1] = work(scale) * (ads @ np.abs(kt))
+                    ek[bi, hi, tok] += work(scale) * (ads.T @ qa)
+                    ev[bi, hi, tok] += u * (p.T @ np.abs(dd[bi, hi, r0:r1]))
+                if roundings:
+                    ds = round_to_dtype(ds, io_dtype)
+                    p = round_to_dtype(p, io_dtype)
                 dq[bi, hi, r0:r1] = work(scale) * (ds @ kt)
                 dk[bi, hi, tok] += work(scale) * (ds.T @ qq[bi, hi, r0:r1])
                 dv[bi, hi, tok] += p.T @ dd[bi, hi, r0:r1]
@@ -454,7 +534,13 @@ def sparse_attn_bwd(
     def merge(x):
         return x.transpose(0, 2, 1, 3).reshape(b, n, c)
 
-    return merge(dq), merge(dk), merge(dv)
+    grads = [merge(dq), merge(dk), merge(dv)]
+    if roundings:
+        grads = [round_to_dtype(x, io_dtype) for x in grads]
+    if envelope:
+        envs = tuple(merge(e) + u * np.abs(x) for e, x in zip((eq, ek, ev), grads))
+        return grads[0], grads[1], grads[2], envs
+    return grads[0], grads[1], grads[2]
 
 
 # --------------------------------------------------------------------------

@@ -63,8 +63,10 @@ def test_api_names_and_signatures(ftk):
                                   "threshold"]
     assert s.parameters["score_block_size"].default == 64 and s.parameters["topk"].default == 16
     s = inspect.signature(ftk.build_qblock_topk_indices)
+    # the reference's five parameters in its order, then this package's optional extension
     assert list(s.parameters) == ["topk_indices", "q_block_size", "q_padding", "topk_scores",
-                                  "qblock_topk"]
+                                  "qblock_topk", "num_score_blocks"]
+    assert s.parameters["num_score_blocks"].default is None
     s = inspect.signature(ftk.flash_topk_attn)
     assert list(s.parameters) == ["q", "k", "v", "merged_indices", "counts", "num_heads",
                                   "q_block_size", "kv_block_size", "scale", "num_kv_heads",

@@ -11,6 +11,7 @@ import os
 
 import numpy as np
 import pytest
+import torch
 
 import cases
 from oracle import ftk_oracle as orc
@@ -228,3 +229,45 @@ def test_first_generation_union_edges():
     assert width == 8 and merged.shape == (1, 1, 3, 8)
     assert merged[0, 0, 0, :3].tolist() == [3, 5, 368] and counts[0, 0].tolist() == [3, 1, 0]
     assert merged[0, 0, 2].tolist() == [-1] * 8 and merged[0, 0, 1, :2].tolist() == [0, -1]
+
+
+def test_round_to_dtype_matches_torch_casts():
+    rng = np.random.default_rng(0)
+    x = (rng.standard_normal(200000) * np.exp(rng.standard_normal(200000) * 6)).astype(np.float32)
+    x[:4] = [0.0, -0.0, 65504.0, 1e-8]
+    t = torch.from_numpy(x)
+    np.testing.assert_array_equal(orc.round_to_dtype(x, "bf16"), t.bfloat16().float().numpy())
+    small = np.clip(x, -6e4, 6e4)
+    np.testing.assert_array_equal(orc.round_to_dtype(small, "fp16"),
+                                  torch.from_numpy(small).half().float().numpy())
+    assert orc.round_to_dtype(x.astype(np.float64), "bf16").dtype == np.float64
+
+
+@pytest.mark.parametrize("name", ["tiny_fp16", "ragged_bf16", "hot_fp16"])
+def test_reference_roundings_mode_and_envelope(name):
+    """The oracle with the reference kernels' roundings (P, dS, delta from the
+    rounded O, stored outputs) stays within the plain bound of the exact oracle
+    on these cases, and within its own first-order worst-case envelope."""
+    import tolerance
+    cfg = cases.GOLDEN_CASES[name]
+    gold = _load(name)
+    t = cases.make_inputs(cfg)
+    x = {k: v.float().numpy() for k, v in t.items()}
+    H, g, kvb = cfg["H"], cfg["q_block_size"], cfg["kv_block_size"]
+    qpad, kvpad = tuple(cfg["q_padding"]), tuple(cfg["kv_padding"])
+    merged = gold["merged"]
+    o_exact, _ = orc.sparse_attn_fwd(x["q"], x["k"], x["v"], merged, H, g, kvb, None, qpad, kvpad)
+    o_stored = orc.round_to_dtype(o_exact, cfg["dtype"])
+    ora = tolerance.attention_oracles(orc, x, merged, H, g, kvb, cfg["dtype"], o_stored, qpad, kvpad)
+    for nm in ("O", "dQ", "dK", "dV"):
+        ex, rd, env = (ora[p][nm] for p in ("exact", "rounded", "envelope"))
+        err = np.abs(rd - ex)
+        assert (err <= ATOL + RTOL * np.abs(ex)).all(), nm
+        # first order: second-order terms and the fp32 store of lse stay below half of it
+        assert (err <= 1.5 * env + 1e-6).all(), (nm, float((err / (env + 1e-12)).max()))
+        assert (env >= 0).all() and np.isfinite(env).all()
+    with pytest.raises(ValueError):
+        orc.sparse_attn_fwd(x["q"], x["k"], x["v"], merged, H, g, kvb, roundings="reference")
+    with pytest.raises(ValueError):
+        orc.sparse_attn_fwd(x["q"], x["k"], x["v"], merged, H, g, kvb, roundings="other",
+                            io_dtype="bf16")
