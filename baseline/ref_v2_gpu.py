@@ -235,7 +235,7 @@ SHAPES = {
 }
 
 
-def time_chain(shape, steps, warmup, heads=None):
+def time_chain(shape, steps, warmup, heads=None, quiet=False):
     """Per-stage and whole-chain CUDA-event times of the reference on one GPU."""
     import torch
     ref = load()
@@ -283,7 +283,8 @@ def time_chain(shape, steps, warmup, heads=None):
             "stage_ms": {n: acc[n] / steps for n in names},
             "tokens_per_s": B * N / (total / steps) * 1e3, "pairs": pairs,
             "gpu": torch.cuda.get_device_name(0)}
-    print(json.dumps(line))
+    if not quiet:
+        print(json.dumps(line))
     return line
 
 

@@ -329,10 +329,34 @@ def run_ours(args):
     del keep
     ftk.check_errors()
 
+    # the same copies with no kernels: what the host <-> device path alone takes per step
+    barrier()
+    c0 = torch.cuda.Event(enable_timing=True)
+    c1 = torch.cuda.Event(enable_timing=True)
+    copy_steps = min(args.steps, 3)
+    c0.record()
+    s_in.wait_stream(cur)
+    s_out.wait_stream(cur)
+    for i in range(copy_steps):
+        with torch.cuda.stream(s_in):
+            for k in ("q", "k", "v", "do"):
+                bufs[i % 2][k].copy_(host[k], non_blocking=True)
+        with torch.cuda.stream(s_out):
+            for nm, src in zip(("o", "dq", "dk", "dv"), ("q", "k", "v", "do")):
+                host_out[nm].copy_(bufs[(i + 1) % 2][src], non_blocking=True)
+    cur.wait_stream(s_out)
+    cur.wait_stream(s_in)
+    c1.record()
+    torch.cuda.synchronize()
+    copy_ms = c0.elapsed_time(c1) / copy_steps
+    for k in devt:
+        devt[k].copy_(host[k])
+    torch.cuda.synchronize()
+
     if dist is not None:
-        tt = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        tt = torch.tensor([ms, e2e_ms, copy_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(tt[0]), float(tt[1])
+        ms, e2e_ms, copy_ms = float(tt[0]), float(tt[1]), float(tt[2])
     tokens_per_step = world * B * N
     value = tokens_per_step * args.steps / (ms / 1e3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
@@ -368,7 +392,7 @@ def run_ours(args):
             "value": value, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "vs_baseline": None, "dtype": cfg.get("dtype", "bf16"), "data": "synthetic",
             "config": {"workload": cfg["name"], "B_per_gpu": B, "N": N, "H": H, "D": D,
                        "score_block_size": b, "topk": K, "threshold": thr, "q_block_size": g,
                        "kv_block_size": kvb, "sharding": "batch x head slices, no collective",
@@ -377,7 +401,10 @@ def run_ours(args):
                        "candidate_pairs_per_step": P},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": bytes_in,
-                    "d2h_bytes_per_step": bytes_out, "ms_per_step": e2e_ms / args.steps},
+                    "d2h_bytes_per_step": bytes_out, "ms_per_step": e2e_ms / args.steps,
+                    "host_copy_only_ms": copy_ms,
+                    "host_copy_only_note": "the step's uploads and downloads alone, no kernels, "
+                                           "both directions at once, max over ranks"},
             "gpu_launches": launches,
             "stage_ms": stage_ms,
             "call_ms": call_ms,
@@ -396,6 +423,10 @@ def run_ours(args):
         }
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(cfg, seconds=args.cpu_seconds)
+        if world == 1 and not args.no_reference_gpu and cfg["name"] == WORKLOAD["name"]:
+            # the reference's own V2 CUDA kernels on this GPU, same shape, in a child process
+            # (both packages are called flash_topk_attn_v2)
+            line["reference_v2_gpu"] = reference_gpu_leg(ms / args.steps)
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
@@ -435,6 +466,7 @@ def cpu_sample_step(cfg, x, rows):
 
 
 def cpu_baseline(cfg, seconds=15.0, rows=512):
+    cores = use_all_host_cores()
     N, H, D = cfg["N"], cfg["H"], cfg["D"]
     g = torch.Generator().manual_seed(0)
     x = [(torch.randn(N, D, generator=g) * cfg["input_scale"]).to(torch.bfloat16).float().numpy()
@@ -449,16 +481,84 @@ def cpu_baseline(cfg, seconds=15.0, rows=512):
         if el > seconds or done >= N:
             break
     # `done` rows of ONE head took `el` seconds; a token needs all H heads
-    return {"value": done / H / el, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+    return {"value": done / H / el, "unit": UNIT, "cores": cores, "kind": "port",
             "sample": f"{done} query rows of one (batch, head) slice, full key length {N}, "
                       f"score+select+merge+sparse fwd+bwd in fp32 numpy ({el:.1f} s); "
                       f"extrapolated to {H} heads"}
+
+
+def use_all_host_cores() -> int:
+    """numpy's BLAS and torch on every core this process may run on; returns the count."""
+    try:
+        import threadpoolctl
+        threadpoolctl.threadpool_limits(limits=HOST_CORES)
+    except Exception:
+        pass
+    torch.set_num_threads(HOST_CORES)
+    return HOST_CORES
+
+
+def reference_gpu_leg(our_ms_per_step, steps=3, warmup=2):
+    """Run `bench.py --impl reference-gpu` as a child and return its line plus the ratio."""
+    if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "flash_topk_attn_v2")):
+        return {"unavailable": "baseline/_ref (the reference install) is absent"}
+    env = dict(os.environ)
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE"):
+        env.pop(k, None)
+    try:
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference-gpu",
+                            "--steps", str(steps), "--warmup", str(warmup)],
+                           capture_output=True, text=True, timeout=1500, env=env, cwd=ROOT)
+        lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+        out = json.loads(lines[-1]) if lines else {"unavailable": (r.stderr or "no output")[-400:]}
+    except Exception as e:  # noqa: BLE001
+        out = {"unavailable": f"{type(e).__name__}: {e}"[:400]}
+    if "ms_per_step" in out:
+        out["speedup_device_timed"] = out["ms_per_step"] / our_ms_per_step
+    return out
+
+
+def run_reference_gpu(args):
+    """The reference's own flash_topk_attn_v2 CUDA path on this GPU, same workload,
+    CUDA-event timed, inputs resident (its extensions rebuilt for sm_100 at run time by
+    baseline/ref_v2_gpu.py; nothing of this repository's kernels is on that path)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    try:
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import ref_v2_gpu
+        if not ref_v2_gpu.available():
+            raise RuntimeError("baseline/_ref (the reference install) is absent")
+        line = ref_v2_gpu.time_chain("headline", args.steps, max(args.warmup, 1), quiet=True)
+    except Exception as e:  # noqa: BLE001
+        print(json.dumps({"impl": "reference-gpu", "unavailable": f"{type(e).__name__}: {e}"[:600]}),
+              flush=True)
+        return
+    cfg = line.pop("config")
+    out = {
+        "impl": "reference-gpu", "metric": METRIC, "value": line["tokens_per_s"], "unit": UNIT,
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 1),
+        "ms_per_step": line["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD["name"], "B_per_gpu": cfg["B"], "N": cfg["N"],
+                   "H": cfg["H"], "D": cfg["D"], "score_block_size": cfg["score_block_size"],
+                   "topk": cfg["topk"], "threshold": cfg["threshold"],
+                   "q_block_size": cfg["q_block_size"], "kv_block_size": cfg["kv_block_size"]},
+        "stage_ms": line["stage_ms"], "candidate_pairs_per_step": line["pairs"],
+        "gpu": line["gpu"],
+        "how": "reference package from baseline/_ref, its CUDA extensions compiled for sm_100 "
+               "with the image's CUTLASS headers (run-time patch, no source edits), CUDA events "
+               "around flash_topk_score -> build_qblock_topk_indices -> flash_topk_attn -> backward",
+    }
+    print(json.dumps(out), flush=True)
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    cores = use_all_host_cores()
     cfg = dict(WORKLOAD)
     N, H, D = cfg["N"], cfg["H"], cfg["D"]
     g = torch.Generator().manual_seed(0)
@@ -484,8 +584,10 @@ def run_reference(args):
         "config": {"workload": cfg["name"], "B_per_gpu": cfg["B"], "N": N, "H": H, "D": D,
                    "score_block_size": cfg["score_block_size"], "topk": cfg["topk"],
                    "threshold": cfg["threshold"], "q_block_size": cfg["q_block_size"],
-                   "kv_block_size": cfg["kv_block_size"]},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+                   "kv_block_size": cfg["kv_block_size"],
+                   "reference_arm": "one process on rank 0's host cores whatever --gpus is: "
+                                    "its value does not grow with N"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -497,7 +599,14 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"],
+                    help="reference = the reference's dense CPU formulation on the host cores; "
+                         "reference-gpu = the reference's own V2 CUDA kernels on this GPU "
+                         "(needs baseline/_ref)")
+    ap.add_argument("--workload", default="config2-e2e", choices=sorted(WORKLOADS),
+                    help="side workloads: the other BASELINE.json shapes (per GPU)")
+    ap.add_argument("--no-reference-gpu", action="store_true",
+                    help="skip the reference-V2-on-this-GPU leg of the default run")
     ap.add_argument("--small", action="store_true", help="N=8192, H=16 (profiling-sized case)")
     ap.add_argument("--head-dim", type=int, default=WORKLOAD["D"],
                     help="head dim other than the headline 128 (profiling / side measurements; "
@@ -507,6 +616,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu(args)
     else:
         run_ours(args)
 
