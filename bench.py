@@ -190,6 +190,9 @@ def run_ours(args):
     cfg = dict(WORKLOADS[args.workload])
     if args.small:
         cfg.update(N=8192, H=16, name="small")
+    if args.seq or args.heads:
+        cfg.update(N=args.seq or cfg["N"], H=args.heads or cfg["H"])
+        cfg["name"] = f"{cfg['name']}-n{cfg['N']}-h{cfg['H']}"
     if args.head_dim != cfg["D"]:
         cfg.update(D=args.head_dim, name=f"{cfg['name']}-d{args.head_dim}")
     H, D, N, B = cfg["H"], cfg["D"], cfg["N"], cfg["B"]
@@ -611,6 +614,8 @@ def main():
     ap.add_argument("--head-dim", type=int, default=WORKLOAD["D"],
                     help="head dim other than the headline 128 (profiling / side measurements; "
                          "the workload name says so)")
+    ap.add_argument("--seq", type=int, default=0, help="sequence length override (profiling)")
+    ap.add_argument("--heads", type=int, default=0, help="head count override (profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     args = ap.parse_args()

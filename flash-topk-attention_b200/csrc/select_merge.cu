@@ -520,8 +520,8 @@ __device__ __forceinline__ void bitonic_desc_blocked(T (&v)[E], int lane) {
 // of the q-block are walked in (row, rank) order, 32 at a time, entries of one
 // step that name the same block are applied in lane order, so every aggregate
 // is the same fp32 sum in the same order.  No block-wide barrier: the warp
-// zeroes its own table in shared memory, adds into it (one match per step finds
-// repeats), builds 64-bit keys (aggregate bits : ~block id) in registers,
+// zeroes its own table in shared memory, adds into it (repeats inside a step
+// are found with a tag table, see below), builds 64-bit keys (aggregate bits : ~block id) in registers,
 // sorts them with the blocked bitonic network and writes its row, the -1 / 0
 // tail with 16-byte stores.
 constexpr int MGW_WARPS = 4;
@@ -533,11 +533,14 @@ qblock_merge_warp_kernel(const int32_t* __restrict__ idx, const float* __restric
                          int32_t* __restrict__ out_idx, float* __restrict__ out_scr,
                          int32_t* __restrict__ counts, int* status) {
   constexpr int MP = 32 * E;
+  constexpr int U = 4;   // steps fetched and checked together
   __shared__ float agg_all[MGW_WARPS][MP];
+  __shared__ uint8_t tag_all[MGW_WARPS][U * MP];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t qb = static_cast<int64_t>(blockIdx.x) * MGW_WARPS + warp;  // bh * QM + m
   if (qb >= total_qb) return;
   float* agg = agg_all[warp];
+  uint8_t* tag = tag_all[warp];
   const int64_t bh = qb / QM;
   const int m = static_cast<int>(qb - bh * QM);
 #pragma unroll
@@ -550,36 +553,65 @@ qblock_merge_warp_kernel(const int32_t* __restrict__ idx, const float* __restric
   if (r1 > r0) {
     const int64_t base = (bh * N + r0) * K;
     const int total = (r1 - r0) * K;
-    constexpr int U = 4;   // steps fetched together
-    for (int e0 = 0; e0 < total; e0 += 32 * U) {
+    // A step is up to 32 consecutive entries; when a row holds fewer than 32
+    // picks a step is one row, so that entries of a step come from one row and
+    // (top-k picks of a row being distinct) name distinct blocks.
+    const int step = K < 32 ? K : 32;
+    // the next batch of U steps is in flight while this one is applied
+    int jn[U];
+    float sn[U];
+    auto fetch = [&](int e0) {
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const int e = e0 + u * step + lane;
+        jn[u] = -1;
+        sn[u] = 0.f;
+        if (lane < step && e < total) {
+          jn[u] = __ldg(idx + base + e);
+          sn[u] = scr ? __ldg(scr + base + e) : 1.f;
+        }
+      }
+    };
+    fetch(0);
+    for (int e0 = 0; e0 < total; e0 += step * U) {
       int jj[U];
       float ss[U];
 #pragma unroll
       for (int u = 0; u < U; u++) {
-        const int e = e0 + u * 32 + lane;
-        jj[u] = -1;
-        ss[u] = 0.f;
-        if (e < total) {
-          jj[u] = __ldg(idx + base + e);
-          ss[u] = scr ? __ldg(scr + base + e) : 1.f;
-        }
+        jj[u] = jn[u];
+        ss[u] = sn[u];
       }
+      if (e0 + step * U < total) fetch(e0 + step * U);
+      // Do two entries of one step name the same block?  Each lane writes its
+      // lane number into the step's tag table at its block id and reads it
+      // back: a lane that finds another lane's number shares its id with it.
+      // (A match instruction answers the same question at many times the cost.)
+      bool lost = false;
 #pragma unroll
       for (int u = 0; u < U; u++) {
-        if (e0 + u * 32 >= total) break;   // warp-uniform
-        int j = jj[u];
-        if (j >= Mtot) {
+        if (jj[u] >= Mtot) {
           if (status) atomicCAS(status, 0, FTK_DEV_BAD_INDEX);
-          j = -1;
+          jj[u] = -1;
         }
+        if (jj[u] >= 0) tag[u * MP + jj[u]] = static_cast<uint8_t>(lane);
+      }
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < U; u++)
+        if (jj[u] >= 0) lost |= tag[u * MP + jj[u]] != static_cast<uint8_t>(lane);
+      const bool repeats = __any_sync(0xffffffffu, lost);
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        if (e0 + u * step >= total) break;   // warp-uniform
+        const int j = jj[u];
         const bool act = j >= 0;
-        const unsigned grp = __match_any_sync(0xffffffffu, act ? j : -1 - lane);
-        const int mult = act ? __popc(grp) : 1;
-        if (__all_sync(0xffffffffu, mult == 1)) {
+        if (!repeats) {
           if (act) agg[j] += ss[u];
         } else {
+          // entries of the step that share a block are applied in lane order
+          const unsigned grp = __match_any_sync(0xffffffffu, act ? j : -1 - lane);
           const int rank = __popc(grp & ((1u << lane) - 1u));
-          const int rounds = redux_max_s32(mult);
+          const int rounds = redux_max_s32(act ? __popc(grp) : 1);
           for (int rd = 0; rd < rounds; rd++) {
             if (act && rank == rd) agg[j] += ss[u];
             __syncwarp();
