@@ -65,6 +65,18 @@ METRIC = "score+sparse fwd+bwd tokens/s @N=32k,H=32,D=128 bf16"
 UNIT = "tokens/s"
 
 
+# DRAM bytes (read + written) per launch and per head, measured with ncu at B=1, N=32768, H=4
+# (profiles/dram_traffic_n32768_h4.txt).  Every kernel works on (batch, head) slices
+# independently, so a launch over B*H slices of this sequence length moves B*H times this.
+DRAM_BYTES_PER_SLICE_N32768 = {
+    "ftk_score_topk": (85.0e6 + 224.0e6 + 269.0e6 + 36.3e6) / 4,
+    "ftk_qblock_merge": (33.7e6 + 33.6e6) / 4,
+    "ftk_sparse_fwd": (118.1e6 + 19.5e6) / 4,
+    "ftk_sparse_bwd_dq": (67.1e6 + 153.3e6 + 19.9e6) / 4,
+    "ftk_sparse_bwd_dkv": (143.6e6 + 41.7e6) / 4,
+}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -413,11 +425,17 @@ def run_ours(args):
             "call_ms": call_ms,
             "roofline": {"bound": "tensor", "kernel": dom, "achieved": kern[dom]["tflops"],
                          "peak": peaks["tf_sus"], "unit": "TFLOP/s",
-                         "frac": kern[dom]["frac"], "traffic": None,
-                         "traffic_note": "tensor-bound kernels: DRAM traffic follows B*H*N*D, not "
-                                         "the pair count, so a small capture does not scale; ncu "
-                                         "at N=8192, H=16: dK/dV 137 MB read + 42 MB written per "
-                                         "launch, 2 % of DRAM bandwidth (profiles/)",
+                         "frac": kern[dom]["frac"],
+                         "traffic": (DRAM_BYTES_PER_SLICE_N32768[dom] * B * H
+                                     if N == 32768 and D == 128 else None),
+                         "traffic_unit": "bytes per launch (DRAM read + written)",
+                         "traffic_note": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one "
+                                         "launch at B=1, N=32768, H=4, times B*H/4: slices are "
+                                         "independent, traffic is proportional to their number "
+                                         "(profiles/dram_traffic_n32768_h4.txt)",
+                         "traffic_all": ({n: v * B * H for n, v in
+                                          DRAM_BYTES_PER_SLICE_N32768.items()}
+                                         if N == 32768 and D == 128 else None),
                          "peak_source": peaks["src"] + " bf16, sustained (kernel timed inside a "
                                         "100 ms step)",
                          "score_frac_of_burst_peak": kern["ftk_score_topk"]["tflops"] / peaks["tf"],
