@@ -22,6 +22,7 @@
 // They return at once when the flag is clear.
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 
 #include "ftk_host.cuh"
 #include "ftk_sm100.cuh"
@@ -320,13 +321,26 @@ score_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
             } else {
               float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
               if (full) {
+                // two columns per instruction for the scaling (fma.f32x2) and for the
+                // running sums (add.f32x2): 2 issue slots per logit instead of 3; the four
+                // partial sums are the same additions in the same order as scalar code
+                float2 s01 = make_float2(0.f, 0.f), s23 = make_float2(0.f, 0.f);
+                const float2 c2 = make_float2(c, c), nm2 = make_float2(-mref, -mref);
 #pragma unroll
                 for (int i = 0; i < 16; i += 4) {
-                  a0 += fast_exp2(fmaf(__uint_as_float(r[hc * 16 + i + 0]), c, -mref));
-                  a1 += fast_exp2(fmaf(__uint_as_float(r[hc * 16 + i + 1]), c, -mref));
-                  a2 += fast_exp2(fmaf(__uint_as_float(r[hc * 16 + i + 2]), c, -mref));
-                  a3 += fast_exp2(fmaf(__uint_as_float(r[hc * 16 + i + 3]), c, -mref));
+                  const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[hc * 16 + i + 0]),
+                                                          __uint_as_float(r[hc * 16 + i + 1])),
+                                              c2, nm2);
+                  const float2 y = __ffma2_rn(make_float2(__uint_as_float(r[hc * 16 + i + 2]),
+                                                          __uint_as_float(r[hc * 16 + i + 3])),
+                                              c2, nm2);
+                  s01 = __fadd2_rn(s01, make_float2(fast_exp2(x.x), fast_exp2(x.y)));
+                  s23 = __fadd2_rn(s23, make_float2(fast_exp2(y.x), fast_exp2(y.y)));
                 }
+                a0 = s01.x;
+                a1 = s01.y;
+                a2 = s23.x;
+                a3 = s23.y;
               } else {
 #pragma unroll
                 for (int i = 0; i < 16; i++) {

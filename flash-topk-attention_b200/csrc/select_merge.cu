@@ -6,19 +6,9 @@
 
 #include "ftk_host.cuh"
 #include "ftk_sm100.cuh"
+#include "select_row.cuh"
 
 namespace ftk {
-
-__device__ __forceinline__ int redux_max_s32(int v) {
-  int r;
-  asm volatile("redux.sync.max.s32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
-  return r;
-}
-__device__ __forceinline__ unsigned redux_min_u32(unsigned v) {
-  unsigned r;
-  asm volatile("redux.sync.min.u32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
-  return r;
-}
 
 // ------------------------------------------------------------------ select
 // One warp per row.  Replaces topk_select_kernel
@@ -113,224 +103,39 @@ topk_select_kernel(const float* __restrict__ scores, const float* __restrict__ r
   }
 }
 
-// Bitonic network over 32*E values held E per lane (position p = r*32 + lane),
-// sorted largest first.  Distances below 32 exchange across lanes, the others
-// between registers of one lane; every index is a compile-time constant.
-template <int E, typename T>
-__device__ __forceinline__ void bitonic_desc(T (&v)[E], int lane) {
-  constexpr int LOGN = (E == 1 ? 5 : E == 2 ? 6 : E == 4 ? 7 : 8);
-#pragma unroll
-  for (int lk = 1; lk <= LOGN; lk++) {
-    const int k = 1 << lk;
-#pragma unroll
-    for (int lj = lk - 1; lj >= 0; lj--) {
-      const int j = 1 << lj;
-      if (j >= 32) {
-        const int jr = j >> 5;
-#pragma unroll
-        for (int r = 0; r < E; r++) {
-          if ((r & jr) == 0) {
-            const bool desc = (((r * 32) & k) == 0);
-            const T x = v[r], y = v[r | jr];
-            const bool sw = desc ? (x < y) : (x > y);
-            v[r] = sw ? y : x;
-            v[r | jr] = sw ? x : y;
-          }
-        }
-      } else {
-#pragma unroll
-        for (int r = 0; r < E; r++) {
-          const T o = __shfl_xor_sync(0xffffffffu, v[r], j);
-          const bool desc = (((r * 32 + lane) & k) == 0);
-          const bool lower = (lane & j) == 0;
-          const bool take_max = (desc == lower);
-          const bool o_gt = o > v[r];
-          v[r] = (take_max == o_gt) ? o : v[r];
-        }
-      }
-    }
-  }
-}
-
-// Sort the compacted candidates (64-bit keys: average bits high, inverted block
-// id low, so larger key = better score, then lower id) and write the first
-// M_out <= 32 of them.  The running sum of raw scores is accumulated in rank
-// order, one addition per rank, exactly like a sequential scan.
-template <int E>
-__device__ __forceinline__ void sorted_emit(const unsigned long long* cand, int count, int lane,
-                                            const float* sraw, int M_out, float threshold,
-                                            int32_t* oi, float* orw, float* oav) {
-  unsigned long long v[E];
-#pragma unroll
-  for (int r = 0; r < E; r++) v[r] = (r * 32 + lane < count) ? cand[r * 32 + lane] : 0ull;
-  bitonic_desc<E>(v, lane);
-  const bool mine = lane < M_out;
-  const unsigned lo = static_cast<unsigned>(v[0]);
-  const int id = static_cast<int>(0xffffffffu - lo);
-  const float avg = __int_as_float(static_cast<int>(v[0] >> 32));
-  const float raw = mine ? sraw[id] : 0.f;
-  float cum = 0.f, mycum = 0.f;
-  for (int p = 0; p < M_out; p++) {
-    cum += __shfl_sync(0xffffffffu, raw, p);
-    if (p == lane) mycum = cum;
-  }
-  const unsigned cutmask = __ballot_sync(0xffffffffu, mine && (mycum >= threshold));
-  const int cutpos = cutmask ? (__ffs(cutmask) - 1) : 32;
-  if (mine) {
-    const bool keep = lane <= cutpos;
-    oi[lane] = keep ? id : -1;
-    orw[lane] = keep ? raw : 0.f;
-    oav[lane] = keep ? avg : 0.f;
-  }
-}
-
-// Register variant for M <= 32 * IPT (IPT a compile-time constant): the lane's
-// IPT averages stay in registers, so the rescan after a pop is a fully
-// unrolled compare/select chain with no shared-memory traffic, and the lane
-// caches its runner-up so that most pops need no rescan at all.  Raw scores
-// still sit in shared memory (one broadcast read per extracted element).
-//
-// When at most 32 entries are wanted the kernel first tries a filter-and-sort
-// path: every lane splits its slots into two groups and takes each group's
-// maximum; the 64 maxima are 64 distinct entries, so the M_out-th largest of
-// them (T) is a lower bound of the M_out-th largest entry overall, and
-// {average >= T} holds every entry the result can contain (ties with T
-// included).  That set is compacted with ballots (about 40 entries for
-// M = 512), sorted as 64-bit keys and written.  The extraction loop below only
-// runs when the set does not fit 128 candidates.
+// (bitonic_desc, sorted_emit and the per-row register select live in select_row.cuh)
+// warps (= rows) per CTA: 8, or 4 where a row's scratch takes 6 KB
 template <int IPT>
-__global__ void __launch_bounds__(SEL_WARPS * 32)
+__host__ __device__ constexpr int sel_wpc() { return IPT >= 32 ? 4 : SEL_WARPS; }
+
+template <int IPT>
+__global__ void __launch_bounds__(sel_wpc<IPT>() * 32)
 topk_select_reg_kernel(const float* __restrict__ scores, const float* __restrict__ row_scale,
                        int64_t rows, int M, int M_out, int bsz, int pad_head, int pad_tail,
                        float threshold, int32_t* __restrict__ out_idx,
                        float* __restrict__ out_raw, float* __restrict__ out_avg) {
-  __shared__ float sraw_all[SEL_WARPS][32 * IPT];
-  __shared__ unsigned long long scand_all[IPT >= 2 ? SEL_WARPS : 1][128];
+  constexpr int WPC = sel_wpc<IPT>();
+  constexpr int CAP = IPT >= 4 ? 256 : 128;
+  __shared__ float sraw_all[WPC][32 * IPT];
+  __shared__ unsigned long long scand_all[IPT >= 2 ? WPC : 1][CAP];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * SEL_WARPS + warp;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * WPC + warp;
   if (row >= rows) return;
-  float* sraw = sraw_all[warp];
-  const float* in = scores + row * M;
   const float inv_total = row_scale ? __frcp_rn(row_scale[row]) : 1.f;
-  const bool pow2 = (bsz & (bsz - 1)) == 0;
-  const float inv_bsz = 1.f / static_cast<float>(bsz);
-  const int NEG = __float_as_int(-1.f);
-
-  int a[IPT];   // average bit patterns (non-negative floats order as ints); NEG = absent
-#pragma unroll
-  for (int i = 0; i < IPT; i++) {
-    const int j = i * 32 + lane;
-    float raw = 0.f, avg = -1.f;
-    if (j < M) {
-      raw = in[j];
-      if (row_scale) raw *= inv_total;
-      int n = bsz;
-      if (j == 0) n -= pad_head;
-      if (j == M - 1) n -= pad_tail;
-      avg = (pow2 && n == bsz) ? raw * inv_bsz : __fdiv_rn(raw, static_cast<float>(n));
-      if (!(avg >= 0.f)) avg = 0.f;
-    }
-    sraw[j] = raw;
-    a[i] = __float_as_int(avg);
-  }
-  // best and runner-up of the lane; ties keep the lower slot (= lower id)
-  int b1 = NEG, i1 = IPT, b2 = NEG, i2 = IPT;
-  auto rescan = [&]() {
-    b1 = NEG; i1 = IPT; b2 = NEG; i2 = IPT;
-#pragma unroll
-    for (int i = 0; i < IPT; i++) {
-      const int v = a[i];
-      if (v > b1) { b2 = b1; i2 = i1; b1 = v; i1 = i; }
-      else if (v > b2) { b2 = v; i2 = i; }
-    }
-  };
-  __syncwarp();
-  int32_t* oi = out_idx + row * M_out;
-  float* orw = out_raw + row * M_out;
-  float* oav = out_avg + row * M_out;
-
-  if constexpr (IPT >= 2) {
-    if (M_out <= 32) {
-      int gm[2] = {NEG, NEG};
-#pragma unroll
-      for (int i = 0; i < IPT; i++) gm[i >= IPT / 2] = max(gm[i >= IPT / 2], a[i]);
-      bitonic_desc<2>(gm, lane);
-      const int T = __shfl_sync(0xffffffffu, gm[0], M_out - 1);
-      if (T >= 0) {
-        unsigned long long* cand = scand_all[warp];
-        const unsigned lt = (1u << lane) - 1u;
-        int count = 0;
-#pragma unroll
-        for (int i = 0; i < IPT; i++) {
-          const bool c = a[i] >= T;
-          const unsigned bal = __ballot_sync(0xffffffffu, c);
-          const int pos = count + __popc(bal & lt);
-          if (c && pos < 128)
-            cand[pos] = (static_cast<unsigned long long>(static_cast<unsigned>(a[i])) << 32) |
-                        (0xffffffffu - static_cast<unsigned>(i * 32 + lane));
-          count += __popc(bal);
-        }
-        __syncwarp();
-        if (count <= 128) {
-          if (count <= 32) sorted_emit<1>(cand, count, lane, sraw, M_out, threshold, oi, orw, oav);
-          else if (count <= 64)
-            sorted_emit<2>(cand, count, lane, sraw, M_out, threshold, oi, orw, oav);
-          else sorted_emit<4>(cand, count, lane, sraw, M_out, threshold, oi, orw, oav);
-          return;
-        }
-      }
-    }
-  }
-  rescan();
-
-  float cum = 0.f;
-  bool cut = false;
-  int hold_idx = -1;
-  float hold_raw = 0.f, hold_avg = 0.f;
-  for (int r = 0; r < M_out; r++) {
-    int w_idx = -1;
-    float w_raw = 0.f, w_avg = 0.f;
-    if (!cut) {
-      const int mx = redux_max_s32(b1);
-      const unsigned cand =
-          (b1 == mx) ? static_cast<unsigned>(i1 * 32 + lane) : 0xffffffffu;
-      const unsigned win = redux_min_u32(cand);
-      w_idx = static_cast<int>(win);
-      w_raw = sraw[win];
-      w_avg = __int_as_float(mx);
-      cum += w_raw;
-      if (cum >= threshold) cut = true;
-      if ((win & 31u) == static_cast<unsigned>(lane)) {
-        // pop: the slot is consumed; promote the runner-up, rescan only when
-        // there is none cached
-#pragma unroll
-        for (int i = 0; i < IPT; i++)
-          if (i == i1) a[i] = NEG;
-        if (i2 < IPT) {
-          b1 = b2; i1 = i2; b2 = NEG; i2 = IPT;
-        } else {
-          rescan();
-        }
-      }
-    }
-    if ((r & 31) == lane) { hold_idx = w_idx; hold_raw = w_raw; hold_avg = w_avg; }
-    if ((r & 31) == 31 || r == M_out - 1) {
-      const int base = r & ~31;
-      if (base + lane <= r) {
-        oi[base + lane] = hold_idx;
-        orw[base + lane] = hold_raw;
-        oav[base + lane] = hold_avg;
-      }
-    }
-  }
+  select_row_reg<IPT, false>(scores + row * M, row_scale != nullptr, inv_total, M, M_out, bsz,
+                             pad_head, pad_tail, threshold, sraw_all[warp],
+                             scand_all[IPT >= 2 ? warp : 0], lane, out_idx + row * M_out,
+                             out_raw + row * M_out, out_avg + row * M_out);
 }
 
 template <int IPT>
 static void launch_select_reg(const float* block_scores, const float* row_scale, int64_t rows,
                               int M, int M_out, int bsz, int pad_head, int pad_tail,
                               float threshold, int32_t* topk_idx, float* topk_raw,
-                              float* topk_avg, unsigned grid, cudaStream_t st) {
-  topk_select_reg_kernel<IPT><<<grid, SEL_WARPS * 32, 0, st>>>(
+                              float* topk_avg, cudaStream_t st) {
+  constexpr int WPC = sel_wpc<IPT>();
+  const unsigned grid = static_cast<unsigned>((rows + WPC - 1) / WPC);
+  topk_select_reg_kernel<IPT><<<grid, WPC * 32, 0, st>>>(
       block_scores, row_scale, rows, M, M_out, bsz, pad_head, pad_tail, threshold, topk_idx,
       topk_raw, topk_avg);
 }
@@ -344,11 +149,11 @@ int select_launch(const float* block_scores, const float* row_scale, int64_t row
   if (M > 4096) return FTK_ERR_UNSUPPORTED;
   const int M_out = max_topk > 0 ? std::min(max_topk, M) : M;
   const int64_t grid = (rows + SEL_WARPS - 1) / SEL_WARPS;
-  if (grid > 0x7fffffffLL) return FTK_ERR_BAD_ARG;
+  if (2 * grid > 0x7fffffffLL) return FTK_ERR_BAD_ARG;
   const unsigned g = static_cast<unsigned>(grid);
 #define FTK_SEL_REG(IPT)                                                                        \
   launch_select_reg<IPT>(block_scores, row_scale, rows, M, M_out, bsz, pad_head, pad_tail,     \
-                         threshold, topk_idx, topk_raw, topk_avg, g, st)
+                         threshold, topk_idx, topk_raw, topk_avg, st)
   if (M <= 32) FTK_SEL_REG(1);
   else if (M <= 64) FTK_SEL_REG(2);
   else if (M <= 128) FTK_SEL_REG(4);

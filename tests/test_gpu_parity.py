@@ -149,8 +149,9 @@ def test_select_merge_reverse_exact(ftk, name):
 
 @pytest.mark.parametrize("M", [33, 40, 64, 100, 257, 512, 1000, 1024, 1500])
 def test_select_paths_exact(ftk, M):
-    """Every select path (filter-and-sort with 32/64/128 candidates, the
-    extraction loop behind it, the shared-memory kernel above M = 1024) against
+    """Every select path (filter-and-sort for up to 32 and up to 64 picks with 32 to
+    256 candidates, the extraction loop behind it, the shared-memory kernel above
+    M = 1024) against
     the oracle: smooth rows, rows with many exact ties, rows whose threshold
     cuts early, padded first/last blocks, flat rows (all candidates tie)."""
     rng = np.random.default_rng(1000 + M)
@@ -163,7 +164,8 @@ def test_select_paths_exact(ftk, M):
     x /= x.sum(-1, keepdims=True)
     scores = torch.from_numpy(x).cuda()
     for b, pad in ((64, (0, 0)), (48, (5, 47))):
-        for thr, k in ((0.9, 32), (0.5, 8), (0.2, 1), (1.5, 17), (0.9, 0), (0.05, 40)):
+        for thr, k in ((0.9, 32), (0.5, 8), (0.2, 1), (1.5, 17), (0.9, 0), (0.05, 40), (1.5, 64),
+                       (0.6, 48), (1.5, 33)):
             gi, gr, ga = ftk.flash_topk_select(scores, thr, k, b, pad)
             oi, orw, oa = orc.topk_select(x, thr, k, b, pad)
             np.testing.assert_array_equal(gi.cpu().numpy(), oi, err_msg=f"{M} {b} {thr} {k}")
