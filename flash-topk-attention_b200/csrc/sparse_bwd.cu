@@ -130,6 +130,7 @@ struct BwdParams {
   int64_t s0_b, s0_n, s0_h, s1_b, s1_n, s1_h;
   int* status;
   int kv_hdiv;               // query heads per kv head (grouped-query attention), 1 otherwise
+  const int32_t* order;      // dKV: kv blocks by fan-in, heaviest first ([BH][Mkv]) or null
 };
 
 // ---------------------------------------------------------------------- dQ
@@ -542,8 +543,22 @@ sparse_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q,
   __shared__ __align__(16) float s_lse2[2][2][128], s_delta[2][2][128];  // [group][parity][q row]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int j0 = blockIdx.x * p.G;          // first kv block of the tile
   const int bh = blockIdx.y;
+  int j0 = blockIdx.x * p.G;                // first kv block of the tile
+  if (p.order) {
+    // Heaviest tiles first: the grid has one CTA per kv block, in the order of
+    // `order` (fan-in descending, ties by lower id); the CTA whose block is the
+    // first of its tile in that order does the tile, the others leave at once.
+    const int32_t* cnt = p.counts + static_cast<int64_t>(bh) * p.Mkv;
+    const int j = p.order[static_cast<int64_t>(bh) * p.Mkv + blockIdx.x];
+    if (j < 0 || j >= p.Mkv) return;
+    j0 = (j / p.G) * p.G;
+    const int cj = cnt[j];
+    for (int jj = j0; jj < min(j0 + p.G, p.Mkv); jj++) {
+      const int cc = cnt[jj];
+      if (jj != j && (cc > cj || (cc == cj && jj < j))) return;
+    }
+  }
   const int b_idx = bh / p.H, h_idx = bh - b_idx * p.H;
   const int groups = min(p.G, p.Mkv - j0);
   const int tile_tok0 = j0 * p.kvb - p.kv_pad_head;
@@ -1004,7 +1019,6 @@ extern "C" int ftk_sparse_bwd_dkv(
     int kv_pad_head, float scale, const float* lse, const float* delta, void* dk, int64_t sdk_b,
     int64_t sdk_n, int64_t sdk_h, void* dv, int64_t sdv_b, int64_t sdv_n, int64_t sdv_h,
     int fwd_list_width, int32_t* status, void* stream) {
-  (void)sorted_kv;  // tiles are issued in block order; kept for interface parity
   if (!q || !k || !v || !dout || !reverse_idx || !reverse_counts || !lse || !delta)
     return FTK_ERR_BAD_ARG;
   int e = bwd_common_checks(dtype, B, H, N, D, QM, q_block_size, kv_block_size, q_pad_head,
@@ -1095,7 +1109,10 @@ extern "C" int ftk_sparse_bwd_dkv(
     return static_cast<size_t>(1024) + static_cast<size_t>(resident) * tile_bytes +
            static_cast<size_t>(nst) * stage_bytes;
   };
-  dim3 grid((M + p.G - 1) / p.G, static_cast<unsigned>(B * H));
+  // one-CTA kernels: tiles in order of fan-in when the caller brings the order
+  const char* oe = getenv("FTK_DKV_ORDER");
+  p.order = (sorted_kv && !(oe && oe[0] == '0')) ? sorted_kv : nullptr;
+  dim3 grid(p.order ? M : (M + p.G - 1) / p.G, static_cast<unsigned>(B * H));
   if (D == 256) {
     const int nst_dv = stages(1), nst_dk = stages(2);
     if (nst_dk < 2) return FTK_ERR_UNSUPPORTED;

@@ -563,3 +563,40 @@ def test_whole_chain_replays_from_a_cuda_graph(ftk):
         ftk.check_errors()
         for name, a, e in zip(("idx", "merged", "o", "lse", "dq", "dk", "dv"), replayed, eager):
             assert torch.equal(a, e), name
+
+
+def test_dkv_tiles_in_fan_in_order_equal_block_order(ftk, monkeypatch):
+    """With short lists dK/dV runs one CTA per tile of kv blocks, heaviest tiles
+    first (the order build_reverse sorted by fan-in; FTK_DKV_ORDER=0 issues them
+    in block order instead).  The order decides when a tile runs, never what it
+    computes: gradients are bit-identical.  Lists: a few hot kv blocks that every
+    q-block names plus random ones, so fan-in is skewed."""
+    H, N, D, g, kvb, W = 2, 2048, 128, 64, 64, 6
+    t = cases.make_inputs(dict(B=1, N=N, H=H, D=D, dtype="bf16", seed=95, do_seed=96))
+    rng = np.random.default_rng(23)
+    QM = M = N // 64
+    merged = np.full((1, H, QM, W), -1, dtype=np.int32)
+    for h in range(H):
+        hot = rng.permutation(M)[:2]
+        for m in range(QM):
+            rest = [j for j in rng.permutation(M)[:W] if j not in set(hot)][:W - 2]
+            merged[0, h, m, :2] = hot
+            merged[0, h, m, 2:2 + len(rest)] = rest
+    mg = torch.from_numpy(merged).cuda()
+
+    def run():
+        q, k, v = (t[n].cuda().requires_grad_(True) for n in "qkv")
+        o, _ = ftk.flash_topk_attn(q, k, v, mg, None, H, g, kvb)
+        o.backward(t["do"].cuda())
+        ftk.check_errors()
+        return k.grad.clone(), v.grad.clone()
+
+    by_fan_in = run()
+    monkeypatch.setenv("FTK_DKV_ORDER", "0")
+    by_block = run()
+    assert torch.equal(by_fan_in[0], by_block[0]) and torch.equal(by_fan_in[1], by_block[1])
+    x = {n: v.float().numpy() for n, v in t.items()}
+    q, k, v = (t[n].cuda().requires_grad_(True) for n in "qkv")
+    o, _ = ftk.flash_topk_attn(q, k, v, mg, None, H, g, kvb)
+    o.backward(t["do"].cuda())
+    _check_grads(x, merged, H, g, kvb, "bf16", o, (q.grad, k.grad, v.grad))
