@@ -88,6 +88,10 @@ def check_errors(device=None) -> None:
         if device is not None and torch.device(device).index not in (None, key):
             continue
         code = int(t.item())
+        snap = _snapshots.get(key)
+        if snap is not None:
+            snap[0][0] = 0
+            snap[1] = None
         if code != 0:
             t.zero_()
             raise RuntimeError(
@@ -95,9 +99,51 @@ def check_errors(device=None) -> None:
             )
 
 
+# A device-side failure (a bounded wait that ran out, a block id out of range)
+# only sets the sticky status word.  So that a caller who never calls
+# check_errors() still hears of it, every operator ends by copying the word to
+# pinned host memory on its stream (4 bytes, no synchronisation) and begins by
+# looking at the copy the previous operator left, if that copy has landed: the
+# failure raises at the next call that finds it, usually one call late.
+# FTK_DEBUG=1 checks synchronously after every operator instead.
+_snapshots = {}
+_deferred = True
+
+
+def deferred_checks(on: bool) -> None:
+    """Switch the look at the previous operator's status copy on or off (on by
+    default).  Off, a device-side failure is only reported by check_errors()."""
+    global _deferred
+    _deferred = bool(on)
+
+
 def _after(device) -> None:
     if _DEBUG:
         check_errors(device)
+        return
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if not _deferred or torch.cuda.is_current_stream_capturing():
+        return
+    snap = _snapshots.get(key)
+    if snap is None:
+        snap = _snapshots[key] = [torch.zeros(1, dtype=torch.int32).pin_memory(), None]
+    host, ev = snap
+    if ev is not None:
+        if not ev.query():
+            return                       # previous copy still in flight: look next time
+        code = int(host[0])
+        if code != 0:
+            host[0] = 0
+            snap[1] = None
+            status_word(dev).zero_()
+            raise RuntimeError(
+                f"flash_topk_attn_v2 device error in an earlier call: {_lib.error_text(code)} "
+                f"(status {code})")
+    host.copy_(status_word(dev), non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream(dev))
+    snap[1] = ev
 
 
 def _next_pow2(x: int) -> int:
@@ -503,17 +549,10 @@ class FlashSparseAttnFunc(torch.autograd.Function):
         H, D, g, kvb, scale, qph, kph, M, Hkv = ctx.meta
         B, N, C = qq.shape
         dev = qq.device
+        _check_backward_blocks(D, g, kvb)
         if D > 128 and (g > 32 or kvb > 32):
             # head dim 256: the gradient kernels hold Q / dO (dQ) or K / V (dK, dV) of 256
             # columns in shared memory and have room for 32-row partner tiles only
-            for name, blk in (("q_block_size", g), ("kv_block_size", kvb)):
-                part = blk
-                while part > 32 and part % 2 == 0:
-                    part //= 2
-                if part > 32 or part % 16 != 0:
-                    raise NotImplementedError(
-                        f"backward at head dim > 128 needs a {name} that halves down to 16 or "
-                        f"32 rows (16, 32, 64, 128), got {blk}")
             merged, g, kvb, qph, kph, M = _split_large_blocks(merged, N, g, kvb, qph, kph, 32)
         do, sdo_b, sdo_n, sdo_h = _as_bnhd(grad_o.to(qq.dtype), False, H, D)
         _, sq_b, sq_n, sq_h = _as_bnhd(qq, False, H, D)
@@ -548,6 +587,24 @@ class FlashSparseAttnFunc(torch.autograd.Function):
             dk = dk.view(B, N, Hkv, grp, D).float().sum(3).to(qq.dtype).view(B, N, Hkv * D)
             dv = dv.view(B, N, Hkv, grp, D).float().sum(3).to(qq.dtype).view(B, N, Hkv * D)
         return dq, dk, dv, None, None, None, None, None, None, None, None, None
+
+
+def _check_backward_blocks(D, g, kvb):
+    """Block sizes the gradient kernels take (the reference's take any q block of
+    1..64 rows and any kv block): multiples of 16 rows, and at head dims above 128
+    sizes that halve down to 16 or 32 rows."""
+    if g % 16 != 0:
+        raise NotImplementedError(
+            f"the backward needs a q_block_size that is a multiple of 16, got {g}")
+    if D > 128:
+        for name, blk in (("q_block_size", g), ("kv_block_size", kvb)):
+            part = blk
+            while part > 32 and part % 2 == 0:
+                part //= 2
+            if part > 32 or part % 16 != 0:
+                raise NotImplementedError(
+                    f"backward at head dim > 128 needs a {name} that halves down to 16 or "
+                    f"32 rows (16, 32, 64, 128), got {blk}")
 
 
 def _split_large_blocks(merged, N, g, kvb, q_pad_head, kv_pad_head, limit=64):
@@ -671,6 +728,9 @@ def flash_sparse_attn(q, k, v, merged_indices, num_heads, q_block_size, kv_block
         (merged_indices, q_block_size, kv_block_size, q_pad_head, kv_pad_head,
          num_kv_blocks) = _split_large_blocks(
             merged_indices, N, q_block_size, kv_block_size, q_pad_head, kv_pad_head)
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        # say so now rather than inside backward()
+        _check_backward_blocks(Dk, q_block_size, kv_block_size)
     o, lse = FlashSparseAttnFunc.apply(
         q, k, v, merged_indices, H, q_block_size, kv_block_size, scale, q_pad_head, kv_pad_head,
         num_kv_blocks, Hkv)

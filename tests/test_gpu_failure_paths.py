@@ -115,7 +115,14 @@ def test_out_of_range_block_id_in_attention_lists(ftk, D, g, kvb, dtype):
                 ftk.check_errors()
         else:
             ftk.check_errors()
-        o.backward(t["do"].cuda())
+        # the operators inside backward() would report the failure themselves as soon as
+        # they see it; switched off here so that the gradients of the bad run can be compared
+        from flash_topk_attn_v2 import ops
+        ops.deferred_checks(False)
+        try:
+            o.backward(t["do"].cuda())
+        finally:
+            ops.deferred_checks(True)
         if expect_error:
             with pytest.raises(RuntimeError, match="105"):
                 ftk.check_errors()
@@ -176,6 +183,29 @@ def test_out_of_range_block_id_in_merge_and_reverse(ftk):
     orev, orc_, oskv = orc.build_reverse_indices(mnp, np.full(mnp.shape[:3], mnp.shape[3]), M)
     np.testing.assert_array_equal(rg[0].cpu().numpy(), orev)
     np.testing.assert_array_equal(rg[1].cpu().numpy(), orc_)
+
+
+def test_device_error_surfaces_at_a_later_call_without_check_errors(ftk):
+    """A caller that never calls check_errors(): every operator leaves a copy of
+    the status word in pinned memory and looks at the previous copy, so the
+    failure of one call raises at a following call."""
+    rng = np.random.default_rng(5)
+    M, K, g = 16, 4, 32
+    idx = np.stack([rng.permutation(M)[:K] for _ in range(2 * 256)]).astype(np.int32)
+    idx = idx.reshape(1, 2, 256, K)
+    good = torch.from_numpy(idx).cuda()
+    bad = good.clone()
+    bad[0, 0, 5, 1] = M + 3
+    ftk.check_errors()
+    ftk.flash_qblock_merge(bad, None, g, g * K, M)          # sets status 105 on the device
+    torch.cuda.synchronize()                                 # the 4-byte copy has landed
+    with pytest.raises(RuntimeError, match="earlier call.*105"):
+        for _ in range(3):
+            ftk.flash_qblock_merge(good, None, g, g * K, M)
+            torch.cuda.synchronize()
+    ftk.flash_qblock_merge(good, None, g, g * K, M)          # cleared: works again
+    torch.cuda.synchronize()
+    ftk.check_errors()
 
 
 def test_max_index_plus1(ftk):

@@ -158,6 +158,10 @@ def test_backward_block_sizes_that_cannot_be_halved(ftk):
     q, k, v = (torch.randn(1, N, H * D, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
                for _ in range(3))
     merged = torch.zeros(1, H, 4, 1, dtype=torch.int32, device="cuda")
-    o, _ = ftk.flash_topk_attn(q, k, v, merged, None, H, 48, 48)
-    with pytest.raises(NotImplementedError):
-        o.sum().backward()
+    # inputs that want gradients: refused at the forward call already
+    with pytest.raises(NotImplementedError, match="halves down"):
+        ftk.flash_topk_attn(q, k, v, merged, None, H, 48, 48)
+    # without gradients the forward itself takes 48-row blocks
+    with torch.no_grad():
+        o, _ = ftk.flash_topk_attn(q, k, v, merged, None, H, 48, 48)
+    assert torch.isfinite(o).all()
