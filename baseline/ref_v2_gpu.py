@@ -235,11 +235,12 @@ SHAPES = {
 }
 
 
-def time_chain(shape, steps, warmup, heads=None, quiet=False):
-    """Per-stage and whole-chain CUDA-event times of the reference on one GPU."""
+def time_chain(shape, steps, warmup, heads=None, quiet=False, cfg=None):
+    """Per-stage and whole-chain CUDA-event times of the reference on one GPU.
+    `cfg` (keys as in SHAPES, optional qblock_topk) overrides the named shape."""
     import torch
     ref = load()
-    cfg = dict(SHAPES[shape])
+    cfg = dict(cfg) if cfg else dict(SHAPES[shape])
     if heads:
         cfg["H"] = heads
     dev = torch.device("cuda", 0)
@@ -261,7 +262,8 @@ def time_chain(shape, steps, warmup, heads=None, quiet=False):
         idx, raw, avg = ref.flash_topk_score(qq.detach(), kk.detach(), H, b, cfg["topk"], (0, 0),
                                              cfg["threshold"])
         ev[1].record()
-        merged, counts, W = ref.build_qblock_topk_indices(idx, g, topk_scores=avg)
+        merged, counts, W = ref.build_qblock_topk_indices(idx, g, topk_scores=avg,
+                                                          qblock_topk=cfg.get("qblock_topk"))
         ev[2].record()
         o, lse = ref.flash_topk_attn(qq, kk, vv, merged, counts, H, g, kvb)
         ev[3].record()

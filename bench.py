@@ -551,7 +551,9 @@ def run_reference_gpu(args):
         import ref_v2_gpu
         if not ref_v2_gpu.available():
             raise RuntimeError("baseline/_ref (the reference install) is absent")
-        line = ref_v2_gpu.time_chain("headline", args.steps, max(args.warmup, 1), quiet=True)
+        wl = {k: v for k, v in WORKLOADS[args.workload].items() if k != "name"}
+        line = ref_v2_gpu.time_chain(args.workload, args.steps, max(args.warmup, 1), quiet=True,
+                                     cfg=wl)
     except Exception as e:  # noqa: BLE001
         print(json.dumps({"impl": "reference-gpu", "unavailable": f"{type(e).__name__}: {e}"[:600]}),
               flush=True)
@@ -561,8 +563,8 @@ def run_reference_gpu(args):
         "impl": "reference-gpu", "metric": METRIC, "value": line["tokens_per_s"], "unit": UNIT,
         "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 1),
         "ms_per_step": line["ms_per_step"], "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD["name"], "B_per_gpu": cfg["B"], "N": cfg["N"],
+        "vs_baseline": None, "dtype": cfg.get("dtype", "bf16"), "data": "synthetic",
+        "config": {"workload": args.workload, "B_per_gpu": cfg["B"], "N": cfg["N"],
                    "H": cfg["H"], "D": cfg["D"], "score_block_size": cfg["score_block_size"],
                    "topk": cfg["topk"], "threshold": cfg["threshold"],
                    "q_block_size": cfg["q_block_size"], "kv_block_size": cfg["kv_block_size"]},

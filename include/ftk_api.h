@@ -7,7 +7,10 @@
  * Conventions
  *   - All pointers are DEVICE pointers unless a name ends in `_host`.
  *   - The caller owns every buffer (inputs, outputs, workspace); the library
- *     allocates nothing and keeps no state between calls.
+ *     allocates nothing and keeps no state between calls.  The one exception
+ *     is ftk_build_reverse_noalloc (see there): its scratch is an array inside
+ *     the library that every call shares, and it caches that array's device
+ *     address per device ordinal.
  *   - Work is enqueued on `stream` (a cudaStream_t passed as void*; NULL is
  *     the legacy default stream) and the call returns without synchronising.
  *   - Return value: FTK_OK or a negative FTK_ERR_* code; nothing is launched
@@ -144,7 +147,8 @@ int ftk_max_index_plus1(const int32_t* idx, int64_t count, int32_t* result, void
 /* Replaces build_reverse_indices_launch (csrc/build_reverse_indices.cpp:3-10,
  * csrc/build_reverse_indices_kernel.cu:71): reverse_idx [BH][M][QM] (-1
  * padded; q-blocks in ascending order), reverse_counts [BH][M],
- * sorted_kv [BH][M] = kv blocks by count descending (ties: lower id).
+ * sorted_kv [BH][M] = kv blocks by count descending (ties: lower id), the
+ * order in which ftk_sparse_bwd_dkv issues its tiles when it is given it.
  * `counts` may be NULL (rows are then read to their full width W; -1 entries
  * are skipped either way).  sorted_kv may be NULL; with it M <= 8192 (the
  * reference stops at 1024).  Workspace: ftk_build_reverse_workspace. */
@@ -168,7 +172,10 @@ int ftk_build_reverse(const int32_t* merged_idx, const int32_t* counts, int64_t 
  * call before any stream capture begins.  All calls share the one array, which
  * is cleared on `stream` at the start of each call: calls whose GPU work can
  * overlap (other streams, other threads) race and must be serialised by the
- * caller. */
+ * caller.  The cached address is kept per device ordinal and belongs to the
+ * device's primary context (the one the runtime API and PyTorch use): it is
+ * not refreshed after cudaDeviceReset and does not follow a caller that
+ * switches between driver-API contexts on one device. */
 size_t ftk_build_reverse_noalloc_capacity(void);
 int ftk_build_reverse_noalloc(const int32_t* merged_idx, const int32_t* counts, int64_t BH,
                               int QM, int W, int M, int32_t* reverse_idx,
@@ -241,7 +248,17 @@ int ftk_sparse_bwd_dq(const void* q, const void* k, const void* v, const void* o
  * caller sums the H / Hkv heads of a group.  `fwd_list_width` is the
  * width W of the merged_idx lists the reverse index was built from (0 if
  * unknown); it only helps to choose between the kernel on pairs of SMs (lists
- * that can cover a good part of the blocks: 4 W >= M) and the one-CTA kernel. */
+ * that can cover a good part of the blocks: 4 W >= M) and the one-CTA kernel.
+ * `sorted_kv` (may be NULL: block order) is the kv-block order of
+ * ftk_build_reverse; the one-CTA kernels issue their tiles in that order,
+ * heaviest first, as the reference's kernel does
+ * (csrc/sparse_attn_bwd_dkv_kernel.cu:43); FTK_DKV_ORDER=0 ignores it.  The
+ * result does not depend on the order.
+ * Block sizes: kv_block_size a multiple of 16 up to 64 in all three attention
+ * calls (the forward takes up to 128), q_block_size a multiple of 16 up to 64
+ * here (any size up to 128 in the forward, up to 64 in dq); the reference takes
+ * any q block of 1..64 rows and any kv block.  Other sizes return
+ * FTK_ERR_UNSUPPORTED. */
 int ftk_sparse_bwd_dkv(const void* q, const void* k, const void* v, const void* dout, int dtype,
                        int64_t B, int64_t H, int64_t Hkv, int64_t N, int64_t D, int64_t sq_b, int64_t sq_n,
                        int64_t sq_h, int64_t sk_b, int64_t sk_n, int64_t sk_h, int64_t sv_b,
