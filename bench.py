@@ -56,6 +56,12 @@ WORKLOADS = {
     "config3": dict(name="config3", B=4, N=8192, H=16, D=128, dtype="bf16", input_scale=1.0,
                     score_block_size=64, topk=16, threshold=1.0, q_block_size=64,
                     kv_block_size=64, qblock_topk=256),
+    # configs[3]: ragged length, virtual padding, hot key blocks, fp16; score + select +
+    # merge only (q blocks of 128 rows: the reference's attention stops at 64)
+    "config4": dict(name="config4", B=2, N=30000, H=32, D=128, dtype="fp16", input_scale=1.0,
+                    score_block_size=128, topk=24, threshold=0.8, q_block_size=128,
+                    kv_block_size=128, qblock_topk=None, padding=(40, 40), q_padding=(40, 40),
+                    attend=False),
     # configs[4]: one batch element (64 of its 512 slices) per GPU
     "config5": dict(name="config5", B=1, N=65536, H=64, D=128, dtype="bf16", input_scale=1.0,
                     score_block_size=64, topk=64, threshold=1.0, q_block_size=64,
@@ -226,13 +232,20 @@ def run_ours(args):
         v = devt["v"].detach().requires_grad_(True)
         if record:
             evs[0].record()
-        idx, raw, avg = ftk.flash_topk_score(q.detach(), k.detach(), H, b, K, (0, 0), thr)
+        idx, raw, avg = ftk.flash_topk_score(q.detach(), k.detach(), H, b, K,
+                                             tuple(cfg.get("padding", (0, 0))), thr)
         if record:
             evs[1].record()
-        merged, counts, W = ftk.build_qblock_topk_indices(idx, g, topk_scores=avg,
-                                                          qblock_topk=cfg["qblock_topk"])
+        merged, counts, W = ftk.build_qblock_topk_indices(
+            idx, g, tuple(cfg.get("q_padding", (0, 0))), avg, cfg["qblock_topk"])
         if record:
             evs[2].record()
+        if not cfg.get("attend", True):
+            # workloads that stop after the merge (configs[3])
+            if record:
+                evs[3].record()
+                evs[4].record()
+            return evs, (merged, None, None, None, counts)
         if before_attn is not None:
             before_attn()          # end-to-end leg: V and dO have arrived
         o, lse = ftk.flash_topk_attn(q, k, v, merged, counts, H, g, kvb)
@@ -310,6 +323,8 @@ def run_ours(args):
         s_out.wait_event(ev)
         with torch.cuda.stream(s_out):
             for nm, t in zip(names, tensors):
+                if t is None:      # workload without attention: nothing to send home
+                    continue
                 host_out[nm].copy_(t, non_blocking=True)
                 t.record_stream(s_out)
 

@@ -109,7 +109,7 @@ template <int IPT>
 __host__ __device__ constexpr int sel_wpc() { return IPT >= 32 ? 4 : SEL_WARPS; }
 
 template <int IPT>
-__global__ void __launch_bounds__(sel_wpc<IPT>() * 32)
+__global__ void __launch_bounds__(sel_wpc<IPT>() * 32, IPT == 16 ? 3 : (IPT == 32 ? 4 : 1))
 topk_select_reg_kernel(const float* __restrict__ scores, const float* __restrict__ row_scale,
                        int64_t rows, int M, int M_out, int bsz, int pad_head, int pad_tail,
                        float threshold, int32_t* __restrict__ out_idx,
@@ -119,13 +119,30 @@ topk_select_reg_kernel(const float* __restrict__ scores, const float* __restrict
   __shared__ float sraw_all[WPC][32 * IPT];
   __shared__ unsigned long long scand_all[IPT >= 2 ? WPC : 1][CAP];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * WPC + warp;
-  if (row >= rows) return;
-  const float inv_total = row_scale ? __frcp_rn(row_scale[row]) : 1.f;
-  select_row_reg<IPT, false>(scores + row * M, row_scale != nullptr, inv_total, M, M_out, bsz,
-                             pad_head, pad_tail, threshold, sraw_all[warp],
-                             scand_all[IPT >= 2 ? warp : 0], lane, out_idx + row * M_out,
-                             out_raw + row * M_out, out_avg + row * M_out);
+  // a warp walks rows warp_id, warp_id + warps, ...; the loads of its next row are in
+  // flight while it works on the current one (the kernel is otherwise bound by their latency)
+  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * WPC;
+  int64_t row = static_cast<int64_t>(blockIdx.x) * WPC + warp;
+  auto fetch = [&](int64_t r, float (&v)[IPT]) {
+    const float* in = scores + r * M;
+#pragma unroll
+    for (int i = 0; i < IPT; i++) {
+      const int j = i * 32 + lane;
+      v[i] = (r < rows && j < M) ? __ldg(in + j) : 0.f;
+    }
+  };
+  float cur[IPT], nxt[IPT];
+  fetch(row, cur);
+  for (; row < rows; row += nwarps) {
+    fetch(row + nwarps, nxt);
+    const float inv_total = row_scale ? __frcp_rn(row_scale[row]) : 1.f;
+    select_row_reg<IPT>(cur, row_scale != nullptr, inv_total, M, M_out, bsz, pad_head, pad_tail,
+                        threshold, sraw_all[warp], scand_all[IPT >= 2 ? warp : 0], lane,
+                        out_idx + row * M_out, out_raw + row * M_out, out_avg + row * M_out);
+    __syncwarp();   // the warp's scratch is free again
+#pragma unroll
+    for (int i = 0; i < IPT; i++) cur[i] = nxt[i];
+  }
 }
 
 template <int IPT>
@@ -134,7 +151,9 @@ static void launch_select_reg(const float* block_scores, const float* row_scale,
                               float threshold, int32_t* topk_idx, float* topk_raw,
                               float* topk_avg, cudaStream_t st) {
   constexpr int WPC = sel_wpc<IPT>();
-  const unsigned grid = static_cast<unsigned>((rows + WPC - 1) / WPC);
+  // a few CTAs per SM, each warp looping over rows
+  const int64_t want = (rows + WPC - 1) / WPC;
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(want, sm_count() * 16LL));
   topk_select_reg_kernel<IPT><<<grid, WPC * 32, 0, st>>>(
       block_scores, row_scale, rows, M, M_out, bsz, pad_head, pad_tail, threshold, topk_idx,
       topk_raw, topk_avg);

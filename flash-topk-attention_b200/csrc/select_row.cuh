@@ -1,5 +1,4 @@
-// Top-k select of one row by one warp, shared by the stand-alone select kernel
-// and the select warps of the fused scoring kernel.
+// Top-k select of one row by one warp (used by topk_select_reg_kernel).
 #pragma once
 
 #include "ftk_sm100.cuh"
@@ -123,13 +122,14 @@ __device__ __forceinline__ void sorted_emit(const unsigned long long* cand, int 
 // M = 512), sorted as 64-bit keys and written.  The extraction loop below only
 // runs when the set does not fit 128 candidates.
 //
-// `in` = the row's M block sums; `scaled`: multiply by `inv_total` first (the
-// fused path keeps unnormalised sums and one reciprocal per row).  `sraw`
-// (32 * IPT floats) and `cand` (128 keys, 256 when IPT >= 4, unused when IPT == 1) are the warp's
-// own shared-memory scratch.  CG: read `in` past L1 (the fused kernel reads
-// what other threads of its CTA have just written).
-template <int IPT, bool CG>
-__device__ __forceinline__ void select_row_reg(const float* __restrict__ in, bool scaled,
+// `rawv` = the lane's slots of the row's M block sums (slot i = block i * 32 +
+// lane, loaded by the caller so that it can have the next row's loads in
+// flight); `scaled`: multiply by `inv_total` first (scoring hands over
+// unnormalised sums and one total per row).  `sraw` (32 * IPT floats) and `cand`
+// (128 keys, 256 when IPT >= 4, unused when IPT == 1) are the warp's own
+// shared-memory scratch.
+template <int IPT>
+__device__ __forceinline__ void select_row_reg(const float (&rawv)[IPT], bool scaled,
                                                float inv_total, int M, int M_out, int bsz,
                                                int pad_head, int pad_tail, float threshold,
                                                float* sraw, unsigned long long* cand, int lane,
@@ -144,7 +144,7 @@ __device__ __forceinline__ void select_row_reg(const float* __restrict__ in, boo
     const int j = i * 32 + lane;
     float raw = 0.f, avg = -1.f;
     if (j < M) {
-      raw = CG ? __ldcg(in + j) : in[j];
+      raw = rawv[i];
       if (scaled) raw *= inv_total;
       int n = bsz;
       if (j == 0) n -= pad_head;
