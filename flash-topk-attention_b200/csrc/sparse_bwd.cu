@@ -27,27 +27,39 @@
 namespace ftk {
 
 // ------------------------------------------------------------------- delta
-// delta[bh][n] = sum_d o * do, one warp per (b, n, h) row.
+// delta[bh][n] = sum_d o * do.  D / 8 lanes per (b, n, h) row, each with one
+// 16-byte load per tensor (rows start on 16-byte boundaries: base pointers are
+// 16-byte aligned and strides multiples of 8 elements), so a warp covers
+// 256 / D rows at once.
 __global__ void delta_kernel(const uint8_t* __restrict__ o, const uint8_t* __restrict__ dout,
                              int fmt, int64_t B, int64_t N, int64_t H, int D, int64_t so_b,
                              int64_t so_n, int64_t so_h, int64_t sd_b, int64_t sd_n, int64_t sd_h,
                              float* __restrict__ delta) {
-  const int64_t row = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const int lpr = D >> 3;                         // lanes per row: 8, 16 or 32
+  const int rpw = 32 / lpr;                       // rows per warp
   const int lane = threadIdx.x & 31;
-  if (row >= B * N * H) return;
-  const int64_t h = row % H, n = (row / H) % N, b = row / (H * N);
-  const uint32_t* po = reinterpret_cast<const uint32_t*>(o + 2 * (b * so_b + n * so_n + h * so_h));
-  const uint32_t* pd =
-      reinterpret_cast<const uint32_t*>(dout + 2 * (b * sd_b + n * sd_n + h * sd_h));
+  const int64_t wid = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const int64_t row = wid * rpw + lane / lpr;
+  const int c = lane % lpr;
   float acc = 0.f;
-  for (int i = lane; i < D / 2; i += 32) {
-    const float2 a = unpack2(po[i], fmt), g = unpack2(pd[i], fmt);
-    acc = fmaf(a.x, g.x, acc);
-    acc = fmaf(a.y, g.y, acc);
-  }
+  if (row < B * N * H) {
+    const int64_t h = row % H, n = (row / H) % N, b = row / (H * N);
+    const uint4 vo = __ldg(reinterpret_cast<const uint4*>(o + 2 * (b * so_b + n * so_n + h * so_h)) + c);
+    const uint4 vd =
+        __ldg(reinterpret_cast<const uint4*>(dout + 2 * (b * sd_b + n * sd_n + h * sd_h)) + c);
+    const uint32_t wo[4] = {vo.x, vo.y, vo.z, vo.w}, wd[4] = {vd.x, vd.y, vd.z, vd.w};
 #pragma unroll
-  for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
-  if (lane == 0) delta[(b * H + h) * N + n] = acc;
+    for (int i = 0; i < 4; i++) {
+      const float2 a = unpack2(wo[i], fmt), g = unpack2(wd[i], fmt);
+      acc = fmaf(a.x, g.x, acc);
+      acc = fmaf(a.y, g.y, acc);
+    }
+  }
+  for (int d = lpr >> 1; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+  if (c == 0 && row < B * N * H) {
+    const int64_t h = row % H, n = (row / H) % N, b = row / (H * N);
+    delta[(b * H + h) * N + n] = acc;
+  }
 }
 
 // dS = 2^(c s - lse2) (dp - delta) for 32 columns of one row, two columns per
@@ -910,13 +922,17 @@ extern "C" int ftk_sparse_bwd_dq(
   if (H % Hkv != 0) return FTK_ERR_BAD_ARG;
   if (q_block_size > 128) return FTK_ERR_UNSUPPORTED;
   if (!aligned_out(dq, sdq_b, sdq_n, sdq_h)) return FTK_ERR_BAD_ARG;
-  if ((so_b | so_n | so_h | sdo_b | sdo_n | sdo_h) & 1) return FTK_ERR_BAD_ARG;
+  // delta reads O and dO with 16-byte loads
+  if ((so_b | so_n | so_h | sdo_b | sdo_n | sdo_h) & 7) return FTK_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(dout)) & 15u)
+    return FTK_ERR_BAD_ARG;
   const int64_t Mkv = (kv_pad_head + N + kv_block_size - 1) / kv_block_size;
   if (Mkv > AT_MAX_BLOCKS) return FTK_ERR_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   const int64_t rows = B * N * H;
-  delta_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, st>>>(
+  const int64_t delta_warps = (rows + 256 / D - 1) / (256 / D);   // 256 / D rows per warp
+  delta_kernel<<<static_cast<unsigned>((delta_warps * 32 + 255) / 256), 256, 0, st>>>(
       static_cast<const uint8_t*>(o), static_cast<const uint8_t*>(dout), dtype, B, N, H,
       static_cast<int>(D), so_b, so_n, so_h, sdo_b, sdo_n, sdo_h, delta);
   if (cudaGetLastError() != cudaSuccess) return FTK_ERR_CUDA;
