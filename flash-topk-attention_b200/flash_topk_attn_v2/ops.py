@@ -119,7 +119,8 @@ def deferred_checks(on: bool) -> None:
 
 def _after(device) -> None:
     if _DEBUG:
-        check_errors(device)
+        if not torch.cuda.is_current_stream_capturing():   # a capture cannot synchronise
+            check_errors(device)
         return
     dev = torch.device(device)
     key = dev.index if dev.index is not None else torch.cuda.current_device()

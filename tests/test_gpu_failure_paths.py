@@ -30,6 +30,10 @@ PROBE = os.path.join(HERE, "native", "libftk_wait_probe.so")
 @pytest.fixture(scope="module")
 def ftk():
     import flash_topk_attn_v2 as m
+    from flash_topk_attn_v2 import ops
+    if ops._DEBUG:
+        pytest.skip("FTK_DEBUG=1 raises inside the failing call; these tests read the status "
+                    "word themselves")
     return m
 
 

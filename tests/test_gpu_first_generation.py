@@ -168,6 +168,10 @@ def test_union_of_wide_id_ranges(v1):
     assert width == ww == 256
     np.testing.assert_array_equal(merged.cpu().numpy(), wm)
     np.testing.assert_array_equal(counts.cpu().numpy(), wc)
+    if ops._DEBUG:      # FTK_DEBUG=1: the cut is reported by the call itself
+        with pytest.raises(RuntimeError):
+            ops.flash_qblock_union(t, g, (12, 0), num_score_blocks=65536, width=8)
+        return
     m2, c2 = ops.flash_qblock_union(t, g, (12, 0), num_score_blocks=65536, width=8)
     np.testing.assert_array_equal(m2.cpu().numpy(), wm[..., :8])
     np.testing.assert_array_equal(c2.cpu().numpy(), np.minimum(wc, 8))
