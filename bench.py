@@ -567,6 +567,8 @@ def run_reference_gpu(args):
         if not ref_v2_gpu.available():
             raise RuntimeError("baseline/_ref (the reference install) is absent")
         wl = {k: v for k, v in WORKLOADS[args.workload].items() if k != "name"}
+        if args.head_dim != wl["D"]:
+            wl["D"] = args.head_dim
         line = ref_v2_gpu.time_chain(args.workload, args.steps, max(args.warmup, 1), quiet=True,
                                      cfg=wl)
     except Exception as e:  # noqa: BLE001
