@@ -211,7 +211,7 @@ def run_ours(args):
     if args.seq or args.heads:
         cfg.update(N=args.seq or cfg["N"], H=args.heads or cfg["H"])
         cfg["name"] = f"{cfg['name']}-n{cfg['N']}-h{cfg['H']}"
-    if args.head_dim != cfg["D"]:
+    if args.head_dim and args.head_dim != cfg["D"]:
         cfg.update(D=args.head_dim, name=f"{cfg['name']}-d{args.head_dim}")
     H, D, N, B = cfg["H"], cfg["D"], cfg["N"], cfg["B"]
     b, K, thr = cfg["score_block_size"], cfg["topk"], cfg["threshold"]
@@ -567,7 +567,7 @@ def run_reference_gpu(args):
         if not ref_v2_gpu.available():
             raise RuntimeError("baseline/_ref (the reference install) is absent")
         wl = {k: v for k, v in WORKLOADS[args.workload].items() if k != "name"}
-        if args.head_dim != wl["D"]:
+        if args.head_dim and args.head_dim != wl["D"]:
             wl["D"] = args.head_dim
         line = ref_v2_gpu.time_chain(args.workload, args.steps, max(args.warmup, 1), quiet=True,
                                      cfg=wl)
@@ -648,7 +648,7 @@ def main():
     ap.add_argument("--no-reference-gpu", action="store_true",
                     help="skip the reference-V2-on-this-GPU leg of the default run")
     ap.add_argument("--small", action="store_true", help="N=8192, H=16 (profiling-sized case)")
-    ap.add_argument("--head-dim", type=int, default=WORKLOAD["D"],
+    ap.add_argument("--head-dim", type=int, default=0,
                     help="head dim other than the headline 128 (profiling / side measurements; "
                          "the workload name says so)")
     ap.add_argument("--seq", type=int, default=0, help="sequence length override (profiling)")
