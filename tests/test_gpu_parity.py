@@ -600,3 +600,29 @@ def test_dkv_tiles_in_fan_in_order_equal_block_order(ftk, monkeypatch):
     o, _ = ftk.flash_topk_attn(q, k, v, mg, None, H, g, kvb)
     o.backward(t["do"].cuda())
     _check_grads(x, merged, H, g, kvb, "bf16", o, (q.grad, k.grad, v.grad))
+
+
+def test_scoring_in_chunks_of_slices_equals_one_call(ftk, monkeypatch):
+    """When the block sums of all (batch, head) slices exceed the scratch budget
+    (4 GiB by default: config 5 needs 17 GB per batch element) the host layer scores
+    the slices in chunks.  Forced here with a tiny budget: three chunks, same bits."""
+    from flash_topk_attn_v2 import ops
+    cfg = dict(B=2, N=640, H=3, D=128, dtype="bf16", seed=97, do_seed=98)
+    t = cases.make_inputs(cfg)
+    q, k = t["q"].cuda(), t["k"].cuda()
+    one = ftk.flash_topk_score(q, k, 3, 64, 4, (0, 0), 0.9)
+    per_slice = ops.lib.ftk_score_topk_workspace(1, 640, 10)
+    monkeypatch.setattr(ops, "_SCORE_SCRATCH_BYTES", 2 * per_slice + 64)
+    calls = []
+    real = ops._call
+
+    def counting(name, fn, *a):
+        calls.append(name)
+        return real(name, fn, *a)
+
+    monkeypatch.setattr(ops, "_call", counting)
+    chunked = ftk.flash_topk_score(q, k, 3, 64, 4, (0, 0), 0.9)
+    ftk.check_errors()
+    assert calls.count("ftk_score_topk") == 3          # 6 slices, 2 per chunk
+    for a, b in zip(one, chunked):
+        assert torch.equal(a, b)
